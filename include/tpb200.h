@@ -1,0 +1,158 @@
+/* tpb200 -- C ABI of the sm_100a reduction and top-k kernels.
+ *
+ * This is the boundary a TensorPlay build binds to replace the CUDA kernels that
+ * p10/src/backend/cuda/ReductionKernels.cu registers for DispatchKey::CUDA (registration block
+ * at ReductionKernels.cu:385-418).  Plain pointers and sizes only; no TensorPlay, PyTorch or C++
+ * types cross it.  The C++ adapter that wraps these calls into kernels with the exact
+ * signatures TensorPlay's DispatchStub expects lives in tensorplay_b200/csrc/adapter/.
+ *
+ * Conventions
+ *   - All data pointers are device pointers on the CUDA device that is current at the call.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream, which is
+ *     where the reference launches everything: ReductionKernels.cu:86-95).
+ *   - Calls only enqueue work; they never synchronise and never allocate device memory.
+ *     Scratch memory is the caller's: ask tpb200_*_workspace_bytes(), pass a buffer of at
+ *     least that size (256-byte aligned).  Its contents need no initialisation.
+ *   - sizes/strides are in ELEMENTS, as in TensorImpl (p10/include/TensorImpl.h:87-98);
+ *     `in` points at the first element (storage offset already applied).  Any strided view
+ *     is accepted; no copy is made.
+ *   - Outputs are written contiguously over the kept dims in their original order
+ *     (keepdim only changes the shape the caller reports, not the layout).
+ *   - Every function returns TPB200_OK or an error code, never throws, never aborts;
+ *     tpb200_last_error() gives the message of the calling thread's last failure.
+ *   - Supported element type: float32 (TPB200_F32).  Other dtypes return
+ *     TPB200_ERR_UNSUPPORTED so that an adapter can fall through to the kernel registered
+ *     before it.
+ */
+#ifndef TPB200_H_
+#define TPB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TPB200_VERSION 100
+
+/* error codes */
+#define TPB200_OK 0
+#define TPB200_ERR_INVALID 1      /* bad argument: message says which                          */
+#define TPB200_ERR_UNSUPPORTED 2  /* dtype / rank not handled by these kernels                 */
+#define TPB200_ERR_DIM_RANGE 3    /* "Dimension out of range" (ReductionKernels.cpp:55-57)     */
+#define TPB200_ERR_EMPTY 4        /* "max(): Expected reduction dim to be non-empty" (:240)    */
+#define TPB200_ERR_WORKSPACE 5    /* workspace missing or too small                            */
+#define TPB200_ERR_CUDA 6         /* a CUDA runtime call failed: "CUDA Error: ..."             */
+
+/* dtypes */
+#define TPB200_F32 0
+
+/* reduction operators.  The first eight replace, one to one, the kernels registered at
+ * ReductionKernels.cu:386-391 and :410-417; the two fused forms serve callers that want
+ * torch-style (values, indices) from one pass (the reference needs max.dim + argmax). */
+#define TPB200_OP_SUM 0        /* sum, sum.dim_IntList        ReductionKernels.cu:227-238 */
+#define TPB200_OP_MEAN 1       /* mean, mean.dim              ReductionKernels.cu:241-253 */
+#define TPB200_OP_VAR 2        /* var, var.dim                ReductionKernels.cu:358-374 */
+#define TPB200_OP_STD 3        /* std, std.dim                ReductionKernels.cu:376-382 */
+#define TPB200_OP_MAX 4        /* max, max.dim (values only)  ReductionKernels.cu:270-281 */
+#define TPB200_OP_MIN 5        /* min, min.dim (values only)  ReductionKernels.cu:284-293 */
+#define TPB200_OP_ARGMAX 6     /* argmax                      ReductionKernels.cu:31-117  */
+#define TPB200_OP_ARGMIN 7     /* argmin                      ReductionKernels.cu:119-121 */
+#define TPB200_OP_MAX_ARGMAX 8 /* values + indices in one pass */
+#define TPB200_OP_MIN_ARGMIN 9
+
+#define TPB200_MAX_DIMS 8
+
+/* Size of one packed partial record (see tpb200_reduce_partial). */
+#define TPB200_PARTIAL_BYTES 40
+
+const char* tpb200_last_error(void);
+int tpb200_version(void);
+
+/* ---- reductions over a dim, several dims, or the whole tensor ---------------------------------
+ * Replaces cuda::{sum,mean,max,min,var,std}[_dim]_kernel and arg_reduce_kernel
+ * (ReductionKernels.cu:54-121, 128-293, 348-382).
+ *
+ *   reduce_mask   bit d set = dim d is reduced; 0 = reduce every dim (the overloads without a
+ *                 dim argument, and an empty dim list)
+ *   index_dim     for ARGMAX/ARGMIN/fused: -1 = position in the flattened (row-major) tensor,
+ *                 as argmax(dim=None) returns; otherwise reduce_mask must be exactly that one
+ *                 dim and the position along it is returned
+ *   correction    var/std: divisor is max(0, n - correction) (ReductionKernels.cu:364-365)
+ *   out_val       float32 results (NULL for ARGMAX/ARGMIN)
+ *   out_idx       int64 results (NULL unless the op returns indices)
+ *
+ * Semantics follow the reference's CPU kernels (p10/src/backend/cpu/ReductionKernels.cpp):
+ * first occurrence wins ties, NaN is never selected by max/min/argmax/argmin, sums are
+ * accumulated in float64 and rounded once.
+ */
+int tpb200_reduce(int op, const void* in, int dtype, int ndim, const int64_t* sizes,
+                  const int64_t* strides, uint64_t reduce_mask, int index_dim, int64_t correction,
+                  void* out_val, int64_t* out_idx, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+size_t tpb200_reduce_workspace_bytes(int op, int dtype, int ndim, const int64_t* sizes,
+                                     const int64_t* strides, uint64_t reduce_mask);
+
+/* ---- top-k along one dim ----------------------------------------------------------------------
+ * New operator (the reference declares none): schema
+ *   topk(Tensor self, int64_t k, int64_t dim=-1, bool largest=true, bool sorted=true)
+ *        -> (Tensor values, Tensor indices)
+ * Contract: the first k entries of each row stably sorted by value (descending if largest,
+ * else ascending), ties in ascending index -- the tie rule of the reference's argmax/argmin
+ * scan (ReductionKernels.cpp:727-735, 793-801), so k = 1 equals argmax/argmin.  -0.0 ties with
+ * +0.0; NaN ranks after every number in both directions; values are returned bit-exact.
+ * sorted = 0 may return the same k entries in any order (this implementation returns them sorted).
+ * out_val / out_idx are written contiguously as [non-selected dims in their original order..., k]:
+ * for dim = last that is the input's shape with dim replaced by k; for another dim the caller
+ * reports the result as a permuted view.  The non-selected dims must collapse to at most two
+ * strided dims; k <= 2048, or any k on rows of at most 16384 elements.
+ */
+int tpb200_topk(const void* in, int dtype, int ndim, const int64_t* sizes, const int64_t* strides,
+                int dim, int64_t k, int largest, int sorted, void* out_val, int64_t* out_idx,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+size_t tpb200_topk_workspace_bytes(int dtype, int ndim, const int64_t* sizes, const int64_t* strides,
+                                   int dim, int64_t k);
+
+/* ---- sharded whole-tensor reductions: per-GPU partial, then a rank-ordered combine ------------
+ * No reference counterpart (the reference is single-GPU: p10/src/backend/cuda/CUDAAllocator.cpp:87-88).
+ *
+ * tpb200_reduce_partial reduces `n` contiguous floats -- this GPU's flat partition, which starts
+ * at element `global_offset` of the whole tensor -- to ONE packed record of TPB200_PARTIAL_BYTES
+ * written at `partial_out` (device memory; typically the slot of this rank in the all-gather
+ * buffer, so the kernel's output is the collective's input with no copy between).
+ *   family:  TPB200_OP_SUM (also serves MEAN), TPB200_OP_VAR (also STD),
+ *            TPB200_OP_MAX_ARGMAX (also MAX, ARGMAX), TPB200_OP_MIN_ARGMIN (also MIN, ARGMIN)
+ * Record layout (little endian): double d0, d1, d2; int64 i0; float f0; uint32 pad
+ *   sum: d0 = sum | var: d0 = count, d1 = mean, d2 = M2 | extremum: f0 = value, i0 = GLOBAL position
+ *
+ * tpb200_reduce_combine merges `n_parts` records in index order (deterministic, independent of
+ * which rank runs it) and writes the result of `op` (any of the ten operators) for a tensor of
+ * `total_count` elements.
+ */
+int tpb200_reduce_partial(int family, const void* in, int dtype, int64_t n, int64_t global_offset,
+                          void* partial_out, void* workspace, size_t workspace_bytes, void* stream);
+
+size_t tpb200_reduce_partial_workspace_bytes(int family, int dtype, int64_t n);
+
+int tpb200_reduce_combine(int op, const void* partials, int n_parts, int64_t total_count,
+                          int64_t correction, void* out_val, int64_t* out_idx, void* stream);
+
+/* ---- global top-k over candidate lists --------------------------------------------------------
+ * Final step of a sharded top-k: `n_cand` candidates (value, int64 GLOBAL index), e.g. the
+ * all-gathered local top-k lists of every GPU, are reduced to the best k under the same order
+ * (value, then ascending index).  n_cand <= 8192.
+ * If list_offsets is not NULL the candidates are `n_cand / list_len` lists of list_len entries
+ * holding list-LOCAL indices, and list_offsets[j] is added to every index of list j (the start of
+ * rank j's partition); with NULL the indices are taken as global already.
+ */
+int tpb200_topk_merge(const float* cand_val, const int64_t* cand_idx, int64_t n_cand, int64_t k,
+                      int largest, const int64_t* list_offsets, int64_t list_len, float* out_val,
+                      int64_t* out_idx, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TPB200_H_ */

@@ -1,0 +1,52 @@
+#!/usr/bin/env bash
+# TEST INFRASTRUCTURE ONLY.  Compiles the reference's own CPU reduction path, from the sources
+# where they lie in a TensorPlay checkout, into oracle/_ref/libtpref.so (binaries only; no
+# reference source is copied into this repository).  The result is used to validate the C
+# restatement in oracle/tp_oracle.c and as the timed CPU baseline.
+#
+# What it runs:
+#   1. the reference's generator  tools/codegen/gen.py  on its two yaml files -- the CPU kernels
+#      call generated Tensor methods (Tensor::mean, operator-, ...), so TensorGenerated.{h,cpp}
+#      is needed; only PyYAML is required;
+#   2. g++ with the reference's own flags (CMakeLists.txt:213,470: -O3 -march=native, OpenMP on,
+#      no USE_CUDA / USE_ONEDNN / USE_MKL) on the P10 core and CPU kernel files;
+#   3. a link with oracle/ref_driver.cpp.
+# The reference's CMake build is not run.  Skips quietly (exit 0) when no checkout is present.
+set -euo pipefail
+HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+REF="${TP_REFERENCE_ROOT:-/root/reference}"
+OUT="$HERE/_ref"
+if [ ! -f "$REF/p10/src/backend/cpu/ReductionKernels.cpp" ]; then
+    echo "build_ref: no TensorPlay checkout at $REF; skipping" >&2
+    exit 0
+fi
+if [ -f "$OUT/libtpref.so" ] && [ "$OUT/libtpref.so" -nt "$HERE/ref_driver.cpp" ] && [ "${1:-}" != "--force" ]; then
+    echo "build_ref: $OUT/libtpref.so is up to date"
+    exit 0
+fi
+mkdir -p "$OUT/gen/tensorplay/ops" "$OUT/pkg" "$OUT/obj"
+python3 "$REF/tools/codegen/gen.py" --yaml "$REF/config/native_functions.yaml" \
+    --derivatives "$REF/config/derivatives.yaml" --out_dir "$OUT/gen/tensorplay/ops" \
+    --pkg_out "$OUT/pkg" > "$OUT/gen.log" 2>&1
+
+CXXFLAGS="-std=c++20 -O3 -march=native -fopenmp -w -fPIC -I$REF/p10/include -I$OUT/gen"
+SRCS=()
+for f in Allocator Device Dispatcher Exception Generator Scalar SizesAndStrides Stacktrace TensorImpl OneDNNContext Tensor; do
+    SRCS+=("$REF/p10/src/$f.cpp")
+done
+for f in Arithmetic Comparison Copy Factory Pointwise Random Reduction View; do
+    SRCS+=("$REF/p10/src/backend/cpu/${f}Kernels.cpp")
+done
+SRCS+=("$OUT/gen/tensorplay/ops/TensorGenerated.cpp")
+
+compile_one() {
+    src="$1"; base="$(basename "${src%.cpp}")"
+    case "$src" in */backend/cpu/*) base="cpu_$base";; esac
+    g++ $CXXFLAGS -c "$src" -o "$OUT/obj/$base.o"
+}
+export -f compile_one
+export CXXFLAGS OUT
+printf '%s\n' "${SRCS[@]}" | xargs -P "$(nproc)" -I{} bash -c 'compile_one "$@"' _ {}
+
+g++ $CXXFLAGS -shared -o "$OUT/libtpref.so" "$HERE/ref_driver.cpp" "$OUT"/obj/*.o -fopenmp
+echo "build_ref: built $OUT/libtpref.so"

@@ -1,0 +1,88 @@
+"""ctypes binding of libtpb200.so (the C ABI declared in include/tpb200.h).
+
+There is no fallback: if the shared library is missing or fails to load, importing an operator
+raises.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libtpb200.so")
+
+# error codes of include/tpb200.h
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_DIM_RANGE, ERR_EMPTY, ERR_WORKSPACE, ERR_CUDA = range(7)
+F32 = 0
+OP = {"sum": 0, "mean": 1, "var": 2, "std": 3, "max": 4, "min": 5, "argmax": 6, "argmin": 7,
+      "max_argmax": 8, "min_argmin": 9}
+PARTIAL_BYTES = 40
+MAX_DIMS = 8
+
+# every symbol include/tpb200.h declares
+SYMBOLS = [
+    "tpb200_last_error", "tpb200_version", "tpb200_reduce", "tpb200_reduce_workspace_bytes",
+    "tpb200_topk", "tpb200_topk_workspace_bytes", "tpb200_reduce_partial",
+    "tpb200_reduce_partial_workspace_bytes", "tpb200_reduce_combine", "tpb200_topk_merge",
+]
+
+_I64P = ctypes.POINTER(ctypes.c_int64)
+_lib = None
+
+
+class Tpb200Error(RuntimeError):
+    """A non-zero status from the C ABI; .code holds the TPB200_ERR_* value."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(msg)
+        self.code = code
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m tensorplay_b200.build` "
+            "(needs nvcc; there is no CPU or PyTorch fallback)")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, i, i64, u64, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64, ctypes.c_size_t
+    L.tpb200_last_error.restype = ctypes.c_char_p
+    L.tpb200_last_error.argtypes = []
+    L.tpb200_version.restype = i
+    L.tpb200_version.argtypes = []
+    L.tpb200_reduce.restype = i
+    L.tpb200_reduce.argtypes = [i, vp, i, i, _I64P, _I64P, u64, i, i64, vp, vp, vp, sz, vp]
+    L.tpb200_reduce_workspace_bytes.restype = sz
+    L.tpb200_reduce_workspace_bytes.argtypes = [i, i, i, _I64P, _I64P, u64]
+    L.tpb200_topk.restype = i
+    L.tpb200_topk.argtypes = [vp, i, i, _I64P, _I64P, i, i64, i, i, vp, vp, vp, sz, vp]
+    L.tpb200_topk_workspace_bytes.restype = sz
+    L.tpb200_topk_workspace_bytes.argtypes = [i, i, _I64P, _I64P, i, i64]
+    L.tpb200_reduce_partial.restype = i
+    L.tpb200_reduce_partial.argtypes = [i, vp, i, i64, i64, vp, vp, sz, vp]
+    L.tpb200_reduce_partial_workspace_bytes.restype = sz
+    L.tpb200_reduce_partial_workspace_bytes.argtypes = [i, i, i64]
+    L.tpb200_reduce_combine.restype = i
+    L.tpb200_reduce_combine.argtypes = [i, vp, i, i64, i64, vp, vp, vp]
+    L.tpb200_topk_merge.restype = i
+    L.tpb200_topk_merge.argtypes = [vp, vp, i64, i64, i, vp, i64, vp, vp, vp]
+    _lib = L
+    return L
+
+
+def i64_array(values):
+    n = max(1, len(values))
+    return (ctypes.c_int64 * n)(*values)
+
+
+def check(rc: int) -> None:
+    """Map a C status to the exception the reference raises for the same condition
+    (p10/include/Exception.h:20-43; messages at p10/src/backend/cpu/ReductionKernels.cpp:55-57,240)."""
+    if rc == OK:
+        return
+    msg = lib().tpb200_last_error().decode()
+    if rc == ERR_UNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise Tpb200Error(rc, msg)

@@ -1,0 +1,277 @@
+// Shared device-side building blocks of the sm_100a reduction and top-k kernels:
+// streaming 128-bit loads, the three accumulator families (fp64 sum, Welford/Chan moments,
+// first-occurrence extremum) with their warp- and block-level combines, and the packed
+// partial record exchanged between kernel passes and between GPUs.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <math.h>
+
+#include "../../include/tpb200.h"
+
+namespace tpb {
+
+constexpr int kWarp = 32;
+constexpr unsigned kFull = 0xffffffffu;
+// "no element selected yet" index: larger than any real position, so a real tie always wins.
+constexpr long long kNoIndex = 0x7fffffffffffffffLL;
+
+// ------------------------------------------------------------------ loads ------------------
+// Input is read exactly once: bypass L1 allocation so the 16-byte sectors stream from L2/HBM.
+__device__ __forceinline__ float4 ld_stream4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ld_stream1(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
+// ------------------------------------------------------------------ async bulk copies ------
+// Global -> shared staging with the bulk-copy engine (cp.async.bulk, non-multicast, into the
+// issuing CTA's own shared memory) completing on an mbarrier.  Source and destination must be
+// 16-byte aligned and the size a multiple of 16 bytes.
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` probes (each probe itself blocks for a hardware-defined
+// short time) and reports false, so a copy that never lands cannot hang the kernel.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity, int limit = 1 << 20) {
+    for (int i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// ------------------------------------------------------------------ packed partial ---------
+// One record per (row, slice) between the two passes of a split reduction, and per GPU in the
+// sharded whole-tensor path (it is the all-gather payload).  Field use by family:
+//   sum/mean : d0 = sum
+//   var/std  : d0 = count, d1 = mean, d2 = M2 (sum of squared deviations from the mean)
+//   extremum : f0 = value, i0 = position (kNoIndex when nothing compared better)
+struct __align__(8) Packed {
+    double d0, d1, d2;
+    long long i0;
+    float f0;
+    unsigned int pad;
+};
+static_assert(sizeof(Packed) == TPB200_PARTIAL_BYTES, "Packed layout is part of the C ABI");
+
+// ------------------------------------------------------------------ accumulators -----------
+// fp64 running sum: every float is widened before the add, so the result is the correctly
+// rounded sum up to ~1e-16 relative to sum|x| -- that is what keeps near-zero row sums within
+// 1e-5 relative of a float64 evaluation.
+struct SumAcc {
+    double s;
+    __device__ __forceinline__ void init() { s = 0.0; }
+    __device__ __forceinline__ void add(float x, long long) { s += (double)x; }
+    __device__ __forceinline__ void finish_thread() {}
+    __device__ __forceinline__ void merge(const SumAcc& o) { s += o.s; }
+    __device__ __forceinline__ SumAcc shfl_down(int d) const {
+        SumAcc r; r.s = __shfl_down_sync(kFull, s, d); return r;
+    }
+    __device__ __forceinline__ void store(Packed* p) const { p->d0 = s; p->d1 = 0; p->d2 = 0; p->i0 = 0; p->f0 = 0; p->pad = 0; }
+    __device__ __forceinline__ void load(const Packed* p) { s = p->d0; }
+};
+
+// Variance.  Inside one thread: moments of (x - K) in fp64, K = the thread's first element
+// (shifted-data form: no per-element division).  finish_thread() turns that into a Welford
+// triple (count, mean, M2); everything above a thread -- lanes, warps, CTAs, slices, GPUs --
+// is combined with Chan's pairwise update, always in a fixed order.
+struct MomAcc {
+    double n, mean, m2;   // after finish_thread(): count, mean, M2
+    double k;             // before: shift; c = count, mean = sum(x-k), m2 = sum((x-k)^2)
+    unsigned int c;
+    __device__ __forceinline__ void init() { n = 0.0; mean = 0.0; m2 = 0.0; k = 0.0; c = 0u; }
+    __device__ __forceinline__ void add(float x, long long) {
+        double xd = (double)x;
+        if (c == 0u) k = xd;
+        double d = xd - k;
+        ++c;
+        mean += d;
+        m2 = fma(d, d, m2);
+    }
+    __device__ __forceinline__ void finish_thread() {
+        n = (double)c;
+        if (c > 0u) {
+            double s1 = mean;
+            mean = k + s1 / n;
+            m2 = m2 - s1 * s1 / n;
+            if (m2 < 0.0) m2 = 0.0;
+        }
+    }
+    __device__ __forceinline__ void merge(const MomAcc& o) {
+        if (o.n == 0.0) return;
+        if (n == 0.0) { n = o.n; mean = o.mean; m2 = o.m2; return; }
+        double nt = n + o.n;
+        double delta = o.mean - mean;
+        double w = o.n / nt;
+        mean = fma(delta, w, mean);
+        m2 = m2 + o.m2 + delta * delta * n * w;
+        n = nt;
+    }
+    __device__ __forceinline__ MomAcc shfl_down(int d) const {
+        MomAcc r;
+        r.n = __shfl_down_sync(kFull, n, d);
+        r.mean = __shfl_down_sync(kFull, mean, d);
+        r.m2 = __shfl_down_sync(kFull, m2, d);
+        r.k = 0.0;
+        r.c = 0u;
+        return r;
+    }
+    __device__ __forceinline__ void store(Packed* p) const { p->d0 = n; p->d1 = mean; p->d2 = m2; p->i0 = 0; p->f0 = 0; p->pad = 0; }
+    __device__ __forceinline__ void load(const Packed* p) { n = p->d0; mean = p->d1; m2 = p->d2; k = 0.0; c = 0u; }
+};
+
+// Extremum with the reference's rule: strict compare, first occurrence wins, NaN never wins
+// (every comparison with NaN is false), -0.0 and +0.0 tie.  Positions grow along a thread's
+// own scan, so the strict compare keeps the thread's first occurrence; between threads a tie
+// goes to the lower position.
+template <bool IS_MAX>
+struct ExtAcc {
+    float v;
+    long long i;
+    __device__ __forceinline__ void init() { v = IS_MAX ? -INFINITY : INFINITY; i = kNoIndex; }
+    __device__ __forceinline__ void add(float x, long long pos) {
+        bool better = IS_MAX ? (x > v) : (x < v);
+        if (better) { v = x; i = pos; }
+    }
+    __device__ __forceinline__ void finish_thread() {}
+    __device__ __forceinline__ void merge(const ExtAcc& o) {
+        bool better = IS_MAX ? (o.v > v) : (o.v < v);
+        if (better || (o.v == v && o.i < i)) { v = o.v; i = o.i; }
+    }
+    __device__ __forceinline__ ExtAcc shfl_down(int d) const {
+        ExtAcc r;
+        r.v = __shfl_down_sync(kFull, v, d);
+        r.i = __shfl_down_sync(kFull, i, d);
+        return r;
+    }
+    __device__ __forceinline__ void store(Packed* p) const { p->d0 = 0; p->d1 = 0; p->d2 = 0; p->i0 = i; p->f0 = v; p->pad = 0; }
+    __device__ __forceinline__ void load(const Packed* p) { v = p->f0; i = p->i0; }
+};
+
+// Fixed-order tree over the 32 lanes; lane 0 holds the result.
+template <class Acc>
+__device__ __forceinline__ void warp_combine(Acc& a) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        Acc o = a.shfl_down(d);
+        a.merge(o);
+    }
+}
+
+// Fixed-order combine over a CTA (blockDim.x threads, multiple of 32, <= 1024); thread 0 holds
+// the result.  `smem` must hold one Acc per warp.
+template <class Acc>
+__device__ __forceinline__ void block_combine(Acc& a, Acc* smem) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    warp_combine(a);
+    if (nwarp == 1) return;
+    if (lane == 0) smem[warp] = a;
+    __syncthreads();
+    if (warp == 0) {
+        if (lane < nwarp) a = smem[lane]; else a.init();
+        warp_combine(a);
+    }
+}
+
+// ------------------------------------------------------------------ epilogues --------------
+// What is written for one finished reduction.  `count` is the number of reduced elements.
+struct Epilogue {
+    int op;               // TPB200_OP_*
+    long long correction; // var/std
+};
+
+__device__ __forceinline__ void write_result(const SumAcc& a, const Epilogue& e, double count, float* ov, long long*, long long o) {
+    // mean of an empty reduction is 0/0 = NaN, as in the reference (sum 0 divided by count 0)
+    ov[o] = e.op == TPB200_OP_MEAN ? (float)(a.s / count) : (float)a.s;
+}
+__device__ __forceinline__ void write_result(const MomAcc& a, const Epilogue& e, double count, float* ov, long long*, long long o) {
+    // divisor max(0, n - correction), division in double, one rounding to float
+    // (p10/src/backend/cpu/ReductionKernels.cpp:824-825, 844-846); an empty tensor gives NaN (:817)
+    double dv = count - (double)e.correction;
+    if (dv < 0.0) dv = 0.0;
+    float var = count == 0.0 ? NAN : (float)(a.m2 / dv);
+    ov[o] = e.op == TPB200_OP_STD ? sqrtf(var) : var;
+}
+template <bool IS_MAX>
+__device__ __forceinline__ void write_result(const ExtAcc<IS_MAX>& a, const Epilogue& e, double, float* ov, long long* oi, long long o) {
+    // nothing compared better (empty, all NaN, or all equal to the start value): index 0 and the
+    // start value, as in the reference's scan (ReductionKernels.cpp:692-694, 727-735)
+    if (ov) ov[o] = a.v;
+    if (oi) oi[o] = a.i == kNoIndex ? 0 : a.i;
+    (void)e;
+}
+
+// ------------------------------------------------------------------ contiguous scan --------
+// Feed `len` contiguous floats at p (any alignment) to acc, split over `nthr` threads with
+// 128-bit loads on the 16-byte aligned body.  `pos0` is the position of p[0] in the reduction's
+// row-major index space.  Each thread sees its elements in ascending position.
+template <int UNROLL, class Acc>
+__device__ __forceinline__ void scan_contig(Acc& acc, const float* __restrict__ p, long long len,
+                                            long long pos0, int tid, int nthr) {
+    // scalar head up to the first 16-byte boundary
+    long long head = (long long)((4 - (((uintptr_t)p >> 2) & 3)) & 3);
+    if (head > len) head = len;
+    for (long long h = tid; h < head; h += nthr) acc.add(ld_stream1(p + h), pos0 + h);
+    const float* q = p + head;
+    const long long nvec = (len - head) >> 2;
+    const long long qpos = pos0 + head;
+    long long i = tid;
+    const long long step = (long long)nthr * UNROLL;
+    // full groups of UNROLL vectors: issue every load before the first use
+    for (; i + (long long)(UNROLL - 1) * nthr < nvec; i += step) {
+        float4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) v[u] = ld_stream4(q + ((i + (long long)u * nthr) << 2));
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            long long b = qpos + ((i + (long long)u * nthr) << 2);
+            acc.add(v[u].x, b); acc.add(v[u].y, b + 1); acc.add(v[u].z, b + 2); acc.add(v[u].w, b + 3);
+        }
+    }
+    for (; i < nvec; i += nthr) {
+        float4 v = ld_stream4(q + (i << 2));
+        long long b = qpos + (i << 2);
+        acc.add(v.x, b); acc.add(v.y, b + 1); acc.add(v.z, b + 2); acc.add(v.w, b + 3);
+    }
+    const long long done = head + (nvec << 2);
+    const long long tail = len - done;
+    for (long long h = tid; h < tail; h += nthr) acc.add(ld_stream1(p + done + h), pos0 + done + h);
+}
+
+}  // namespace tpb

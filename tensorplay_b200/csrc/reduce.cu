@@ -1,0 +1,692 @@
+// Reductions (sum / mean / var / std / max / min / argmax / argmin and the fused value+index
+// forms) for float32 tensors on sm_100a, behind tpb200_reduce and the sharded partial/combine
+// entry points.  Replaces cuda::*_kernel of p10/src/backend/cuda/ReductionKernels.cu:54-382
+// (one thread per row for argmax, cudnnReduceTensor for the rest, a 6-launch composition for var).
+//
+// Every kernel is HBM-bound: the input is read exactly once with 128-bit streaming loads, the
+// strided view is consumed in place (no .contiguous() copy), and the arithmetic per element is a
+// handful of instructions.  A host-side planner canonicalises (sizes, strides, reduce mask) into
+// one of four kernel families:
+//
+//   ROW      the innermost reduced dim is contiguous: a row is `nseg` runs of `seglen` floats
+//            - row_warp_kernel : one warp per row            (short rows, many rows)
+//            - row_cta_kernel  : one CTA per row             (rows of a few KB .. a few hundred KB)
+//            - row_split_kernel + finalize_kernel : S CTAs per row, fixed slices, then a
+//              fixed-order combine of the S packed partials  (few very long rows, whole tensor)
+//   COL      the innermost KEPT dim is contiguous, one reduced dim strides over it:
+//            col_kernel (each thread owns 4 adjacent columns, 16-byte loads stay coalesced along
+//            the kept dim) (+ col_finalize_kernel when the reduced dim is split over CTAs)
+//   GENERIC  anything else (and empty reductions): one warp per output, div/mod addressing
+//
+// All combines run in a fixed order, so results are bit-reproducible run to run.
+#include "common.cuh"
+#include "host_util.h"
+
+#include <algorithm>
+#include <vector>
+
+namespace tpb {
+
+// ------------------------------------------------------------------ geometry ---------------
+struct RowGeom {
+    long long rows;                      // number of outputs
+    long long k1;                        // size of the inner kept dim (rows = k0 * k1)
+    long long ks0, ks1;                  // element strides of the outer / inner kept dim
+    long long nseg, seglen, seg_stride;  // one row = nseg runs of seglen contiguous floats
+};
+
+struct GenGeom {
+    int nk, nr;
+    long long ksize[TPB200_MAX_DIMS], kstride[TPB200_MAX_DIMS];
+    long long rsize[TPB200_MAX_DIMS], rstride[TPB200_MAX_DIMS];
+    long long outs, count;
+};
+
+__device__ __forceinline__ const float* row_base(const float* in, const RowGeom& g, long long r) {
+    long long a = r / g.k1;
+    long long b = r - a * g.k1;
+    return in + a * g.ks0 + b * g.ks1;
+}
+
+template <class Acc>
+__device__ __forceinline__ void add4(Acc& acc, const float4& v, long long b) {
+    acc.add(v.x, b); acc.add(v.y, b + 1); acc.add(v.z, b + 2); acc.add(v.w, b + 3);
+}
+
+// ------------------------------------------------------------------ ROW: warp per row ------
+template <class Acc>
+__global__ void __launch_bounds__(256)
+row_warp_kernel(const float* __restrict__ in, RowGeom g, Epilogue e, float* ov, long long* oi) {
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= g.rows) return;
+    const float* p = row_base(in, g, r);
+    Acc acc;
+    acc.init();
+    for (long long s = 0; s < g.nseg; ++s)
+        scan_contig<4>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
+    acc.finish_thread();
+    warp_combine(acc);
+    if (lane == 0) write_result(acc, e, (double)g.nseg * (double)g.seglen, ov, oi, r);
+}
+
+// ------------------------------------------------------------------ ROW: CTA per row -------
+// tps = threads that share one run (power of two).  With several runs per row the CTA is a
+// (tps x blockDim/tps) grid of threads: x walks along a run, y over runs, and loads of four
+// different runs are issued together so a thread always has 64 bytes in flight.
+template <class Acc>
+__global__ void __launch_bounds__(512)
+row_cta_kernel(const float* __restrict__ in, RowGeom g, int tps, int vec_ok, Epilogue e, float* ov,
+               long long* oi) {
+    __shared__ Acc sm[32];
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const long long r = blockIdx.x;
+    const float* p = row_base(in, g, r);
+    Acc acc;
+    acc.init();
+    if (g.nseg == 1) {
+        scan_contig<4>(acc, p, g.seglen, 0, tid, nthr);
+    } else {
+        const int tx = tid & (tps - 1);
+        const int ty = tid / tps;
+        const int ny = nthr / tps;
+        const long long sv = g.seglen >> 2;
+        if (vec_ok && sv <= tps) {
+            for (long long s = ty; s < g.nseg; s += 4LL * ny) {
+                float4 v[4];
+                bool ok[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    long long ss = s + (long long)u * ny;
+                    ok[u] = ss < g.nseg && tx < sv;
+                    if (ok[u]) v[u] = ld_stream4(p + ss * g.seg_stride + 4 * tx);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    long long ss = s + (long long)u * ny;
+                    if (ok[u]) add4(acc, v[u], ss * g.seglen + 4 * tx);
+                }
+            }
+        } else {
+            for (long long s = ty; s < g.nseg; s += ny)
+                scan_contig<2>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, tx, tps);
+        }
+    }
+    acc.finish_thread();
+    block_combine(acc, sm);
+    if (tid == 0) write_result(acc, e, (double)g.nseg * (double)g.seglen, ov, oi, r);
+}
+
+// ------------------------------------------------------------------ ROW: split rows --------
+// Pass 1: CTA (s, r) reduces the fixed slice [s*chunk, (s+1)*chunk) of row r to one packed partial.
+template <class Acc>
+__global__ void __launch_bounds__(512)
+row_split_kernel(const float* __restrict__ in, RowGeom g, long long chunk, Packed* ws) {
+    __shared__ Acc sm[32];
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const long long s = blockIdx.x, r = blockIdx.y, S = gridDim.x;
+    const float* p = row_base(in, g, r);
+    const long long begin = s * chunk;
+    long long end = begin + chunk;
+    if (end > g.seglen) end = g.seglen;
+    Acc acc;
+    acc.init();
+    if (begin < end) scan_contig<4>(acc, p + begin, end - begin, begin, tid, nthr);
+    acc.finish_thread();
+    block_combine(acc, sm);
+    if (tid == 0) acc.store(&ws[r * S + s]);
+}
+
+// Pass 2: one warp per row merges that row's S partials in a fixed order (lane l takes
+// l, l+32, ..., then the lane tree).  Writes the finished result, or -- for the sharded path --
+// one packed record whose position is shifted to the tensor-global index space.
+template <class Acc>
+__global__ void __launch_bounds__(128)
+finalize_kernel(const Packed* __restrict__ ws, long long rows, int S, double count, Epilogue e,
+                float* ov, long long* oi, Packed* packed_out, long long idx_offset) {
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    Acc acc;
+    acc.init();
+    acc.finish_thread();
+    for (int s = lane; s < S; s += 32) {
+        Acc o;
+        o.load(&ws[r * S + s]);
+        acc.merge(o);
+    }
+    warp_combine(acc);
+    if (lane == 0) {
+        if (packed_out) {
+            Packed out;
+            acc.store(&out);
+            if (out.i0 != kNoIndex) out.i0 += idx_offset;
+            packed_out[r] = out;
+        } else {
+            write_result(acc, e, count, ov, oi, r);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ COL --------------------
+// Input viewed as [O, L, I] with I contiguous and kept, L reduced.  blockIdx.x = tile + tiles*o,
+// blockIdx.y = slice of L.  Thread (tx, ty) owns VEC adjacent columns and walks L with stride ny,
+// four rows in flight.  Cross-ty combine is a fixed tree in shared memory.
+template <class Acc, int VEC>
+__global__ void __launch_bounds__(256)
+col_kernel(const float* __restrict__ in, long long o_stride, long long L, long long l_stride,
+           long long I, int tiles, int tx_n, long long lchunk, Packed* ws, Epilogue e, float* ov,
+           long long* oi) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Acc* sm = reinterpret_cast<Acc*>(smem_raw);
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int tx = tid & (tx_n - 1), ty = tid / tx_n, ny = nthr / tx_n;
+    const long long o = blockIdx.x / tiles;
+    const int tile = (int)(blockIdx.x - o * tiles);
+    const int s = blockIdx.y, S = gridDim.y;
+    const long long i0 = ((long long)tile * tx_n + tx) * VEC;
+    const bool active = i0 < I;
+    const float* base = in + o * o_stride + i0;
+    const long long l0 = (long long)s * lchunk;
+    long long l1 = l0 + lchunk;
+    if (l1 > L) l1 = L;
+
+    Acc acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v].init();
+
+    if (active) {
+        for (long long l = l0 + ty; l < l1; l += 4LL * ny) {
+            if (VEC == 4) {
+                float4 x[4];
+                bool ok[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    long long ll = l + (long long)u * ny;
+                    ok[u] = ll < l1;
+                    if (ok[u]) x[u] = ld_stream4(base + ll * l_stride);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    long long ll = l + (long long)u * ny;
+                    if (ok[u]) {
+                        acc[0].add(x[u].x, ll);
+                        acc[VEC > 1 ? 1 : 0].add(x[u].y, ll);
+                        acc[VEC > 2 ? 2 : 0].add(x[u].z, ll);
+                        acc[VEC > 3 ? 3 : 0].add(x[u].w, ll);
+                    }
+                }
+            } else {
+                float x[4];
+                bool ok[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    long long ll = l + (long long)u * ny;
+                    ok[u] = ll < l1;
+                    if (ok[u]) x[u] = ld_stream1(base + ll * l_stride);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    long long ll = l + (long long)u * ny;
+                    if (ok[u]) acc[0].add(x[u], ll);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v].finish_thread();
+
+    for (int stride = ny >> 1; stride >= 1; stride >>= 1) {
+        if (ty >= stride && ty < 2 * stride) {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) sm[((ty - stride) * tx_n + tx) * VEC + v] = acc[v];
+        }
+        __syncthreads();
+        if (ty < stride) {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v].merge(sm[(ty * tx_n + tx) * VEC + v]);
+        }
+        __syncthreads();
+    }
+    if (ty == 0 && active) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            if (ws) acc[v].store(&ws[(o * S + s) * I + i0 + v]);
+            else write_result(acc[v], e, (double)L, ov, oi, o * I + i0 + v);
+        }
+    }
+}
+
+template <class Acc>
+__global__ void __launch_bounds__(256)
+col_finalize_kernel(const Packed* __restrict__ ws, long long O, int S, long long I, double count,
+                    Epilogue e, float* ov, long long* oi) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= O * I) return;
+    const long long o = t / I, i = t - o * I;
+    Acc acc;
+    acc.load(&ws[(o * S) * I + i]);
+    for (int s = 1; s < S; ++s) {
+        Acc b;
+        b.load(&ws[(o * S + s) * I + i]);
+        acc.merge(b);
+    }
+    write_result(acc, e, count, ov, oi, t);
+}
+
+// ------------------------------------------------------------------ GENERIC ----------------
+// One warp per output; addresses from a div/mod walk over the kept and the reduced dims.  Correct
+// for every strided view (and for empty reductions: count = 0 leaves the start value).
+template <class Acc>
+__global__ void __launch_bounds__(256)
+generic_kernel(const float* __restrict__ in, GenGeom g, Epilogue e, float* ov, long long* oi) {
+    const int lane = threadIdx.x & 31;
+    const long long o = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (o >= g.outs) return;
+    long long off = 0, q = o;
+    for (int d = g.nk - 1; d >= 0; --d) {
+        long long c = q % g.ksize[d];
+        q /= g.ksize[d];
+        off += c * g.kstride[d];
+    }
+    Acc acc;
+    acc.init();
+    for (long long j = lane; j < g.count; j += 32) {
+        long long roff = 0, jj = j;
+        for (int d = g.nr - 1; d >= 0; --d) {
+            long long c = jj % g.rsize[d];
+            jj /= g.rsize[d];
+            roff += c * g.rstride[d];
+        }
+        acc.add(ld_stream1(in + off + roff), j);
+    }
+    acc.finish_thread();
+    warp_combine(acc);
+    if (lane == 0) write_result(acc, e, (double)g.count, ov, oi, o);
+}
+
+// ------------------------------------------------------------------ planner ----------------
+enum Family { FAM_SUM, FAM_MOM, FAM_MAX, FAM_MIN };
+enum Strategy { ST_NONE, ST_ROW_WARP, ST_ROW_CTA, ST_ROW_SPLIT, ST_COL, ST_GENERIC };
+
+struct Plan {
+    Strategy st = ST_NONE;
+    RowGeom row{};
+    GenGeom gen{};
+    // row
+    int threads = 256, tps = 1, vec_ok = 0;
+    int S = 1;
+    long long chunk = 0;
+    // col
+    long long O = 1, o_stride = 0, L = 0, l_stride = 0, I = 0, lchunk = 0;
+    int tiles = 1, tx_n = 1, vec = 1;
+    long long outs = 0, count = 0;
+    size_t ws_bytes = 0;
+};
+
+static int family_of(int op, Family* f) {
+    switch (op) {
+        case TPB200_OP_SUM: case TPB200_OP_MEAN: *f = FAM_SUM; return 0;
+        case TPB200_OP_VAR: case TPB200_OP_STD: *f = FAM_MOM; return 0;
+        case TPB200_OP_MAX: case TPB200_OP_ARGMAX: case TPB200_OP_MAX_ARGMAX: *f = FAM_MAX; return 0;
+        case TPB200_OP_MIN: case TPB200_OP_ARGMIN: case TPB200_OP_MIN_ARGMIN: *f = FAM_MIN; return 0;
+        default: return 1;
+    }
+}
+
+struct Dim { long long size, stride; };
+
+static void push_merged(std::vector<Dim>& v, Dim d) {
+    if (!v.empty() && v.back().stride == d.stride * d.size) {
+        v.back().size *= d.size;
+        v.back().stride = d.stride;
+    } else {
+        v.push_back(d);
+    }
+}
+
+// Environment override for experiments: TPB200_FORCE_STRATEGY = warp | cta | split | col | generic
+static Strategy forced_strategy() {
+    const char* s = getenv("TPB200_FORCE_STRATEGY");
+    if (!s) return ST_NONE;
+    std::string v(s);
+    if (v == "warp") return ST_ROW_WARP;
+    if (v == "cta") return ST_ROW_CTA;
+    if (v == "split") return ST_ROW_SPLIT;
+    if (v == "col") return ST_COL;
+    if (v == "generic") return ST_GENERIC;
+    return ST_NONE;
+}
+
+static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64_t* strides,
+                     uint64_t mask, Plan* pl) {
+    if (ndim < 0 || ndim > TPB200_MAX_DIMS)
+        return fail(TPB200_ERR_UNSUPPORTED, "tensors of rank %d are not supported (max %d)", ndim, TPB200_MAX_DIMS);
+    if (ndim > 0 && (!sizes || !strides)) return fail(TPB200_ERR_INVALID, "sizes/strides must not be NULL");
+    if (ndim < 64 && (mask >> ndim) != 0 && ndim > 0) return fail(TPB200_ERR_DIM_RANGE, "Dimension out of range");
+    if (ndim == 0 && mask > 1) return fail(TPB200_ERR_DIM_RANGE, "Dimension out of range");
+    const uint64_t all = ndim == 0 ? 0 : ((ndim == 64) ? ~0ull : ((1ull << ndim) - 1));
+    if (mask == 0 || ndim == 0) mask = all;
+
+    std::vector<Dim> kept, red;
+    long long outs = 1, count = 1;
+    for (int d = 0; d < ndim; ++d) {
+        if (sizes[d] < 0) return fail(TPB200_ERR_INVALID, "negative size in dim %d", d);
+        const bool r = (mask >> d) & 1;
+        if (r) count *= sizes[d]; else outs *= sizes[d];
+        if (sizes[d] == 1) continue;
+        push_merged(r ? red : kept, Dim{sizes[d], strides[d]});
+    }
+    pl->outs = outs;
+    pl->count = count;
+    if (outs == 0) { pl->st = ST_NONE; return TPB200_OK; }
+
+    const Strategy force = forced_strategy();
+    const int sms = sm_count();
+    const bool ptr16 = (((uintptr_t)in) & 15) == 0;
+
+    auto use_generic = [&]() {
+        GenGeom& g = pl->gen;
+        g.nk = (int)kept.size();
+        g.nr = (int)red.size();
+        for (int i = 0; i < g.nk; ++i) { g.ksize[i] = kept[i].size; g.kstride[i] = kept[i].stride; }
+        for (int i = 0; i < g.nr; ++i) { g.rsize[i] = red[i].size; g.rstride[i] = red[i].stride; }
+        g.outs = outs;
+        g.count = count;
+        pl->st = ST_GENERIC;
+        return TPB200_OK;
+    };
+    if (count == 0 || force == ST_GENERIC) return use_generic();
+    if (red.empty()) red.push_back(Dim{1, 1});  // every reduced dim has size 1: rows of one element
+
+    const bool row_ok = red.back().stride == 1 && red.size() <= 2 && kept.size() <= 2;
+    const bool col_ok = red.size() == 1 && !kept.empty() && kept.back().stride == 1 && kept.size() <= 2;
+
+    if (row_ok && force != ST_COL) {
+        RowGeom& g = pl->row;
+        g.rows = outs;
+        g.seglen = red.back().size;
+        g.nseg = red.size() == 2 ? red[0].size : 1;
+        g.seg_stride = red.size() == 2 ? red[0].stride : 0;
+        if (kept.size() == 2) { g.k1 = kept[1].size; g.ks0 = kept[0].stride; g.ks1 = kept[1].stride; }
+        else if (kept.size() == 1) { g.k1 = 1; g.ks0 = kept[0].stride; g.ks1 = 0; }
+        else { g.k1 = 1; g.ks0 = 0; g.ks1 = 0; }
+        const long long L = g.nseg * g.seglen;
+        pl->vec_ok = ptr16 && g.ks0 % 4 == 0 && g.ks1 % 4 == 0 && g.seg_stride % 4 == 0 && g.seglen % 4 == 0;
+
+        // split: few rows, each long enough to feed many CTAs
+        int S = 1;
+        if (g.nseg == 1 && outs <= 65535) {
+            long long want = ceil_div((long long)sms * 16, outs);
+            long long most = L / 16384;
+            S = (int)std::max(1LL, std::min(std::min(want, most), 1LL << 20));
+        }
+        Strategy st;
+        if (force == ST_ROW_SPLIT && g.nseg == 1 && outs <= 65535) { st = ST_ROW_SPLIT; S = std::max(S, 2); }
+        else if (force == ST_ROW_WARP) st = ST_ROW_WARP;
+        else if (force == ST_ROW_CTA) st = ST_ROW_CTA;
+        else if (S >= 2) st = ST_ROW_SPLIT;
+        else if (g.nseg == 1 && L <= 1024) st = ST_ROW_WARP;
+        else st = ST_ROW_CTA;
+
+        pl->st = st;
+        if (st == ST_ROW_SPLIT) {
+            pl->S = S;
+            pl->chunk = round_up(ceil_div(L, S), 4);
+            pl->S = (int)ceil_div(L, pl->chunk);
+            pl->threads = 512;
+            pl->ws_bytes = (size_t)outs * pl->S * sizeof(Packed);
+        } else if (st == ST_ROW_CTA) {
+            pl->threads = L <= 2048 ? 128 : (L <= 16384 ? 256 : 512);
+            pl->tps = g.nseg == 1 ? pl->threads : std::min(pl->threads, pow2_ceil(std::max(1LL, g.seglen / 4)));
+        }
+        return TPB200_OK;
+    }
+    if (col_ok) {
+        pl->st = ST_COL;
+        pl->I = kept.back().size;
+        pl->L = red[0].size;
+        pl->l_stride = red[0].stride;
+        if (kept.size() == 2) { pl->O = kept[0].size; pl->o_stride = kept[0].stride; }
+        else { pl->O = 1; pl->o_stride = 0; }
+        pl->vec = (ptr16 && pl->I % 4 == 0 && pl->o_stride % 4 == 0 && pl->l_stride % 4 == 0) ? 4 : 1;
+        pl->tx_n = std::min(32, pow2_ceil(ceil_div(pl->I, pl->vec)));
+        pl->tiles = (int)ceil_div(pl->I, (long long)pl->tx_n * pl->vec);
+        const int ny = 256 / pl->tx_n;
+        long long ctas = pl->O * pl->tiles;
+        long long want = ceil_div((long long)sms * 8, ctas);
+        long long most = std::max(1LL, pl->L / ((long long)ny * 8));
+        int S = (int)std::max(1LL, std::min(std::min(want, most), 65535LL));
+        pl->lchunk = ceil_div(pl->L, S);
+        pl->S = (int)ceil_div(pl->L, pl->lchunk);
+        if (pl->S > 1) pl->ws_bytes = (size_t)pl->O * pl->S * pl->I * sizeof(Packed);
+        if (pl->O * pl->tiles > 0x7fffffffLL) return use_generic();
+        return TPB200_OK;
+    }
+    return use_generic();
+}
+
+template <class Acc>
+static int launch_plan(const Plan& pl, const float* in, Epilogue e, float* ov, long long* oi,
+                       void* ws, cudaStream_t st) {
+    switch (pl.st) {
+        case ST_NONE:
+            return TPB200_OK;
+        case ST_ROW_WARP: {
+            unsigned grid = (unsigned)ceil_div(pl.row.rows, 8);
+            row_warp_kernel<Acc><<<grid, 256, 0, st>>>(in, pl.row, e, ov, oi);
+            TPB_LAUNCH_OK("row_warp_kernel");
+            return TPB200_OK;
+        }
+        case ST_ROW_CTA: {
+            if (pl.row.rows > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
+            row_cta_kernel<Acc><<<(unsigned)pl.row.rows, pl.threads, 0, st>>>(in, pl.row, pl.tps, pl.vec_ok, e, ov, oi);
+            TPB_LAUNCH_OK("row_cta_kernel");
+            return TPB200_OK;
+        }
+        case ST_ROW_SPLIT: {
+            dim3 grid((unsigned)pl.S, (unsigned)pl.row.rows);
+            row_split_kernel<Acc><<<grid, pl.threads, 0, st>>>(in, pl.row, pl.chunk, (Packed*)ws);
+            TPB_LAUNCH_OK("row_split_kernel");
+            unsigned fg = (unsigned)ceil_div(pl.row.rows, 4);
+            finalize_kernel<Acc><<<fg, 128, 0, st>>>((const Packed*)ws, pl.row.rows, pl.S, (double)pl.count, e, ov, oi, nullptr, 0);
+            TPB_LAUNCH_OK("finalize_kernel");
+            return TPB200_OK;
+        }
+        case ST_COL: {
+            const int ny = 256 / pl.tx_n;
+            dim3 grid((unsigned)(pl.O * pl.tiles), (unsigned)pl.S);
+            Packed* w = pl.S > 1 ? (Packed*)ws : nullptr;
+            if (pl.vec == 4) {
+                size_t sm = (size_t)std::max(1, ny / 2) * pl.tx_n * 4 * sizeof(Acc);
+                col_kernel<Acc, 4><<<grid, 256, sm, st>>>(in, pl.o_stride, pl.L, pl.l_stride, pl.I, pl.tiles, pl.tx_n, pl.lchunk, w, e, ov, oi);
+            } else {
+                size_t sm = (size_t)std::max(1, ny / 2) * pl.tx_n * sizeof(Acc);
+                col_kernel<Acc, 1><<<grid, 256, sm, st>>>(in, pl.o_stride, pl.L, pl.l_stride, pl.I, pl.tiles, pl.tx_n, pl.lchunk, w, e, ov, oi);
+            }
+            TPB_LAUNCH_OK("col_kernel");
+            if (pl.S > 1) {
+                unsigned fg = (unsigned)ceil_div(pl.O * pl.I, 256);
+                col_finalize_kernel<Acc><<<fg, 256, 0, st>>>((const Packed*)ws, pl.O, pl.S, pl.I, (double)pl.count, e, ov, oi);
+                TPB_LAUNCH_OK("col_finalize_kernel");
+            }
+            return TPB200_OK;
+        }
+        case ST_GENERIC: {
+            unsigned grid = (unsigned)ceil_div(pl.gen.outs, 8);
+            generic_kernel<Acc><<<grid, 256, 0, st>>>(in, pl.gen, e, ov, oi);
+            TPB_LAUNCH_OK("generic_kernel");
+            return TPB200_OK;
+        }
+    }
+    return fail(TPB200_ERR_INVALID, "internal: no strategy");
+}
+
+static int check_ws(const Plan& pl, void* ws, size_t ws_bytes) {
+    if (pl.ws_bytes == 0) return TPB200_OK;
+    if (!ws || ws_bytes < pl.ws_bytes)
+        return fail(TPB200_ERR_WORKSPACE, "workspace of %zu bytes required, %zu given", pl.ws_bytes, ws ? ws_bytes : (size_t)0);
+    if (((uintptr_t)ws) & 7) return fail(TPB200_ERR_WORKSPACE, "workspace must be 8-byte aligned");
+    return TPB200_OK;
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+extern "C" size_t tpb200_reduce_workspace_bytes(int op, int dtype, int ndim, const int64_t* sizes,
+                                                const int64_t* strides, uint64_t reduce_mask) {
+    (void)op;
+    if (dtype != TPB200_F32) return 0;
+    Plan pl;
+    // alignment of the data pointer does not change the workspace size
+    if (make_plan((const void*)16, ndim, sizes, strides, reduce_mask, &pl) != TPB200_OK) return 0;
+    return pl.ws_bytes;
+}
+
+extern "C" int tpb200_reduce(int op, const void* in, int dtype, int ndim, const int64_t* sizes,
+                             const int64_t* strides, uint64_t reduce_mask, int index_dim,
+                             int64_t correction, void* out_val, int64_t* out_idx, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+    Family fam;
+    if (family_of(op, &fam)) return fail(TPB200_ERR_INVALID, "unknown reduction operator %d", op);
+    if (dtype != TPB200_F32) return fail(TPB200_ERR_UNSUPPORTED, "only float32 input is supported (dtype code %d)", dtype);
+    const bool wants_val = !(op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN);
+    const bool wants_idx = op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN || op == TPB200_OP_MAX_ARGMAX || op == TPB200_OP_MIN_ARGMIN;
+    Plan pl;
+    int rc = make_plan(in, ndim, sizes, strides, reduce_mask, &pl);
+    if (rc) return rc;
+    if (wants_idx) {
+        const uint64_t all = ndim == 0 ? 0 : ((1ull << ndim) - 1);
+        if (index_dim < 0) {
+            if (!(reduce_mask == 0 || reduce_mask == all))
+                return fail(TPB200_ERR_INVALID, "a flat index needs every dim reduced");
+        } else {
+            if (index_dim >= ndim) return fail(TPB200_ERR_DIM_RANGE, "Dimension out of range");
+            if (reduce_mask != (1ull << index_dim))
+                return fail(TPB200_ERR_INVALID, "index_dim must be the one reduced dim");
+        }
+    }
+    if (pl.outs == 0) return TPB200_OK;
+    if (wants_val && (fam == FAM_MAX || fam == FAM_MIN) && pl.count == 0 && reduce_mask == 0) {
+        // the overload without a dim argument on an empty tensor (ReductionKernels.cpp:240, :326);
+        // with an explicit dim list the reference fills the output with the start value instead
+        return fail(TPB200_ERR_EMPTY, "%s(): Expected reduction dim to be non-empty", fam == FAM_MAX ? "max" : "min");
+    }
+    if (!in && pl.count > 0) return fail(TPB200_ERR_INVALID, "input pointer is NULL");
+    if (wants_val && !out_val) return fail(TPB200_ERR_INVALID, "out_val is NULL");
+    if (wants_idx && !out_idx) return fail(TPB200_ERR_INVALID, "out_idx is NULL");
+    rc = check_ws(pl, workspace, workspace_bytes);
+    if (rc) return rc;
+
+    Epilogue e{op, (long long)correction};
+    float* ov = wants_val ? (float*)out_val : nullptr;
+    long long* oi = wants_idx ? (long long*)out_idx : nullptr;
+    cudaStream_t st = (cudaStream_t)stream;
+    const float* x = (const float*)in;
+    switch (fam) {
+        case FAM_SUM: return launch_plan<SumAcc>(pl, x, e, ov, oi, workspace, st);
+        case FAM_MOM: return launch_plan<MomAcc>(pl, x, e, ov, oi, workspace, st);
+        case FAM_MAX: return launch_plan<ExtAcc<true>>(pl, x, e, ov, oi, workspace, st);
+        case FAM_MIN: return launch_plan<ExtAcc<false>>(pl, x, e, ov, oi, workspace, st);
+    }
+    return fail(TPB200_ERR_INVALID, "internal: bad family");
+}
+
+// ---------------------------------------------------------------- sharded whole tensor ------
+namespace tpb {
+
+static void flat_plan(const void* in, int64_t n, Plan* pl) {
+    const int sms = sm_count();
+    RowGeom& g = pl->row;
+    g.rows = 1; g.k1 = 1; g.ks0 = 0; g.ks1 = 0; g.nseg = 1; g.seglen = n; g.seg_stride = 0;
+    long long S = std::max(1LL, std::min((long long)sms * 16, (long long)(n / 16384)));
+    pl->chunk = round_up(ceil_div(std::max<long long>(n, 1), S), 4);
+    pl->S = (int)std::max(1LL, ceil_div((long long)n, pl->chunk));
+    pl->threads = 512;
+    pl->outs = 1;
+    pl->count = n;
+    pl->ws_bytes = (size_t)pl->S * sizeof(Packed);
+    pl->st = ST_ROW_SPLIT;
+    (void)in;
+}
+
+template <class Acc>
+static int launch_partial(const Plan& pl, const float* in, long long offset, Packed* out, void* ws,
+                          cudaStream_t st) {
+    dim3 grid((unsigned)pl.S, 1);
+    row_split_kernel<Acc><<<grid, pl.threads, 0, st>>>(in, pl.row, pl.chunk, (Packed*)ws);
+    TPB_LAUNCH_OK("row_split_kernel");
+    Epilogue e{0, 0};
+    finalize_kernel<Acc><<<1, 32, 0, st>>>((const Packed*)ws, 1, pl.S, (double)pl.count, e, nullptr, nullptr, out, offset);
+    TPB_LAUNCH_OK("finalize_kernel");
+    return TPB200_OK;
+}
+
+template <class Acc>
+static int launch_combine(const Packed* parts, int n, double count, Epilogue e, float* ov,
+                          long long* oi, cudaStream_t st) {
+    finalize_kernel<Acc><<<1, 32, 0, st>>>(parts, 1, n, count, e, ov, oi, nullptr, 0);
+    TPB_LAUNCH_OK("finalize_kernel");
+    return TPB200_OK;
+}
+
+}  // namespace tpb
+
+extern "C" size_t tpb200_reduce_partial_workspace_bytes(int family, int dtype, int64_t n) {
+    (void)family;
+    if (dtype != TPB200_F32 || n < 0) return 0;
+    Plan pl;
+    flat_plan(nullptr, n, &pl);
+    return pl.ws_bytes;
+}
+
+extern "C" int tpb200_reduce_partial(int family, const void* in, int dtype, int64_t n,
+                                     int64_t global_offset, void* partial_out, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+    Family fam;
+    if (family_of(family, &fam)) return fail(TPB200_ERR_INVALID, "unknown reduction family %d", family);
+    if (dtype != TPB200_F32) return fail(TPB200_ERR_UNSUPPORTED, "only float32 input is supported (dtype code %d)", dtype);
+    if (n < 0) return fail(TPB200_ERR_INVALID, "negative element count");
+    if (!partial_out) return fail(TPB200_ERR_INVALID, "partial_out is NULL");
+    if (n > 0 && !in) return fail(TPB200_ERR_INVALID, "input pointer is NULL");
+    if (((uintptr_t)partial_out) & 7) return fail(TPB200_ERR_INVALID, "partial_out must be 8-byte aligned");
+    Plan pl;
+    flat_plan(in, n, &pl);
+    int rc = check_ws(pl, workspace, workspace_bytes);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const float* x = (const float*)in;
+    Packed* out = (Packed*)partial_out;
+    switch (fam) {
+        case FAM_SUM: return launch_partial<SumAcc>(pl, x, global_offset, out, workspace, st);
+        case FAM_MOM: return launch_partial<MomAcc>(pl, x, global_offset, out, workspace, st);
+        case FAM_MAX: return launch_partial<ExtAcc<true>>(pl, x, global_offset, out, workspace, st);
+        case FAM_MIN: return launch_partial<ExtAcc<false>>(pl, x, global_offset, out, workspace, st);
+    }
+    return fail(TPB200_ERR_INVALID, "internal: bad family");
+}
+
+extern "C" int tpb200_reduce_combine(int op, const void* partials, int n_parts, int64_t total_count,
+                                     int64_t correction, void* out_val, int64_t* out_idx, void* stream) {
+    Family fam;
+    if (family_of(op, &fam)) return fail(TPB200_ERR_INVALID, "unknown reduction operator %d", op);
+    if (n_parts < 1 || !partials) return fail(TPB200_ERR_INVALID, "need at least one partial record");
+    const bool wants_val = !(op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN);
+    const bool wants_idx = op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN || op == TPB200_OP_MAX_ARGMAX || op == TPB200_OP_MIN_ARGMIN;
+    if (wants_val && !out_val) return fail(TPB200_ERR_INVALID, "out_val is NULL");
+    if (wants_idx && !out_idx) return fail(TPB200_ERR_INVALID, "out_idx is NULL");
+    Epilogue e{op, (long long)correction};
+    float* ov = wants_val ? (float*)out_val : nullptr;
+    long long* oi = wants_idx ? (long long*)out_idx : nullptr;
+    cudaStream_t st = (cudaStream_t)stream;
+    const Packed* p = (const Packed*)partials;
+    const double cnt = (double)total_count;
+    switch (fam) {
+        case FAM_SUM: return launch_combine<SumAcc>(p, n_parts, cnt, e, ov, oi, st);
+        case FAM_MOM: return launch_combine<MomAcc>(p, n_parts, cnt, e, ov, oi, st);
+        case FAM_MAX: return launch_combine<ExtAcc<true>>(p, n_parts, cnt, e, ov, oi, st);
+        case FAM_MIN: return launch_combine<ExtAcc<false>>(p, n_parts, cnt, e, ov, oi, st);
+    }
+    return fail(TPB200_ERR_INVALID, "internal: bad family");
+}

@@ -1,0 +1,205 @@
+"""Host-side mirror of TensorPlay's reduction operators on top of the tpb200 C ABI.
+
+Names, argument meaning and error behaviour follow the reference's Tensor methods
+(src/bindings/python/Tensor.cpp:1102-1225; schema config/native_functions.yaml:695-794):
+
+    sum(x, dim=None, keepdim=False, *, dtype=None)      mean(...) likewise
+    var(x, dim=None, correction=1, keepdim=False)       std(...) likewise
+    max(x, dim=None, keepdim=False)  -> values only, as max.dim in the reference
+    min(...)                            (native_functions.yaml:720-733)
+    argmax(x, dim=None, keepdim=False)                  argmin(...) likewise
+    topk(x, k, dim=-1, largest=True, sorted=True) -> (values, indices)   [new operator]
+    max_with_indices / min_with_indices(x, dim, keepdim=False) -> (values, indices), one pass
+
+`dim` may be an int, a list of ints (sum/mean/var/std/max/min) or None.  Tensors are torch CUDA
+tensors: torch is used for device memory and streams only; every number is produced by the
+sm_100a kernels in libtpb200.so.  Strided views are consumed in place.
+"""
+from __future__ import annotations
+
+import builtins as _py
+
+import torch
+
+from . import _lib
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
+    """Per (device, stream) scratch buffer, grown on demand and reused across calls."""
+    if nbytes == 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(_py.max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _check_input(x: torch.Tensor, what: str) -> None:
+    if not isinstance(x, torch.Tensor):
+        raise TypeError(f"{what}: expected a tensor")
+    if not x.is_cuda:
+        raise RuntimeError(f"{what}: tpb200 kernels run on CUDA tensors only (got {x.device}); there is no CPU path")
+    if x.dtype != torch.float32:
+        raise NotImplementedError(f"{what} not implemented for this dtype ({x.dtype}); float32 only")
+    if x.dim() > _lib.MAX_DIMS:
+        raise NotImplementedError(f"{what}: tensors of rank {x.dim()} are not supported")
+
+
+def _dims_mask(x: torch.Tensor, dim) -> tuple[int, list[int]]:
+    """(reduce mask, normalised dims); mask 0 = whole tensor.  Out-of-range raises like
+    compute_reduction_shape (p10/src/backend/cpu/ReductionKernels.cpp:48-58)."""
+    if dim is None:
+        return 0, list(range(x.dim()))
+    dims = [dim] if isinstance(dim, int) else list(dim)
+    if len(dims) == 0:
+        return 0, list(range(x.dim()))
+    nd = x.dim()
+    out, mask = [], 0
+    for d in dims:
+        d = int(d)
+        dd = d + nd if d < 0 else d
+        if dd < 0 or dd >= _py.max(nd, 1):
+            raise RuntimeError("Dimension out of range")
+        if nd == 0:
+            continue
+        mask |= 1 << dd
+        if dd not in out:
+            out.append(dd)
+    return mask, out
+
+
+def _out_shape(x: torch.Tensor, dims: list[int], keepdim: bool) -> list[int]:
+    shape = []
+    for i, s in enumerate(x.shape):
+        if i in dims:
+            if keepdim:
+                shape.append(1)
+        else:
+            shape.append(s)
+    return shape
+
+
+def _reduce(op: str, x: torch.Tensor, dim, keepdim: bool, correction: int = 1, index_dim: int = -1):
+    _check_input(x, op)
+    mask, dims = _dims_mask(x, dim)
+    L = _lib.lib()
+    nd = x.dim()
+    sizes = _lib.i64_array(list(x.shape))
+    strides = _lib.i64_array(list(x.stride()))
+    shape = _out_shape(x, dims, keepdim)
+    want_val = op not in ("argmax", "argmin")
+    want_idx = op in ("argmax", "argmin", "max_argmax", "min_argmin")
+    with torch.cuda.device(x.device):
+        ov = torch.empty(shape, dtype=torch.float32, device=x.device) if want_val else None
+        oi = torch.empty(shape, dtype=torch.int64, device=x.device) if want_idx else None
+        nbytes = L.tpb200_reduce_workspace_bytes(_lib.OP[op], _lib.F32, nd, sizes, strides, mask)
+        ws = _workspace(x.device, nbytes)
+        rc = L.tpb200_reduce(
+            _lib.OP[op], x.data_ptr(), _lib.F32, nd, sizes, strides, mask, index_dim, int(correction),
+            ov.data_ptr() if want_val else None, oi.data_ptr() if want_idx else None,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc)
+    if want_val and want_idx:
+        return ov, oi
+    return ov if want_val else oi
+
+
+def _check_dtype(dtype, what):
+    if dtype is not None and dtype != torch.float32:
+        raise NotImplementedError(f"{what}: only dtype=float32 (or None) is supported")
+
+
+def sum(x, dim=None, keepdim=False, *, dtype=None):
+    _check_dtype(dtype, "sum")
+    return _reduce("sum", x, dim, keepdim)
+
+
+def mean(x, dim=None, keepdim=False, *, dtype=None):
+    _check_dtype(dtype, "mean")
+    return _reduce("mean", x, dim, keepdim)
+
+
+def var(x, dim=None, correction=1, keepdim=False):
+    return _reduce("var", x, dim, keepdim, correction)
+
+
+def std(x, dim=None, correction=1, keepdim=False):
+    return _reduce("std", x, dim, keepdim, correction)
+
+
+def max(x, dim=None, keepdim=False):
+    return _reduce("max", x, dim, keepdim)
+
+
+def min(x, dim=None, keepdim=False):
+    return _reduce("min", x, dim, keepdim)
+
+
+def _arg(op, x, dim, keepdim):
+    if dim is None:
+        return _reduce(op, x, None, False, index_dim=-1)
+    if not isinstance(dim, int):
+        raise TypeError(f"{op}(): dim must be an int or None")
+    nd = x.dim()
+    d = dim + nd if dim < 0 else dim
+    if d < 0 or d >= _py.max(nd, 1):
+        raise RuntimeError("Dimension out of range")
+    if nd == 0:
+        return _reduce(op, x, None, False, index_dim=-1)
+    return _reduce(op, x, d, keepdim, index_dim=d)
+
+
+def argmax(x, dim=None, keepdim=False):
+    return _arg("argmax", x, dim, keepdim)
+
+
+def argmin(x, dim=None, keepdim=False):
+    return _arg("argmin", x, dim, keepdim)
+
+
+def max_with_indices(x, dim, keepdim=False):
+    """(max.dim values, argmax indices) from one pass over the input."""
+    return _arg("max_argmax", x, dim, keepdim)
+
+
+def min_with_indices(x, dim, keepdim=False):
+    return _arg("min_argmin", x, dim, keepdim)
+
+
+def topk(x, k, dim=-1, largest=True, sorted=True):
+    """First k entries of each row along `dim`, stably sorted by value (descending if largest),
+    ties in ascending index.  Returns (values float32, indices int64)."""
+    _check_input(x, "topk")
+    nd = x.dim()
+    d = dim + nd if dim < 0 else dim
+    if d < 0 or d >= _py.max(nd, 1):
+        raise RuntimeError("Dimension out of range")
+    L = _lib.lib()
+    sizes = _lib.i64_array(list(x.shape))
+    strides = _lib.i64_array(list(x.stride()))
+    shape = list(x.shape)
+    if nd:
+        shape[d] = int(k)
+    with torch.cuda.device(x.device):
+        ov = torch.empty(shape, dtype=torch.float32, device=x.device)
+        oi = torch.empty(shape, dtype=torch.int64, device=x.device)
+        nbytes = L.tpb200_topk_workspace_bytes(_lib.F32, nd, sizes, strides, d, int(k))
+        ws = _workspace(x.device, nbytes)
+        # outputs are written as [rows..., k] with k innermost; move k back to `dim` afterwards
+        inner_shape = [s for i, s in enumerate(x.shape) if i != d] + [int(k)]
+        ov_c = ov if d == nd - 1 or nd == 0 else torch.empty(inner_shape, dtype=torch.float32, device=x.device)
+        oi_c = oi if d == nd - 1 or nd == 0 else torch.empty(inner_shape, dtype=torch.int64, device=x.device)
+        rc = L.tpb200_topk(
+            x.data_ptr(), _lib.F32, nd, sizes, strides, d, int(k), int(bool(largest)), int(bool(sorted)),
+            ov_c.data_ptr(), oi_c.data_ptr(), ws.data_ptr() if ws is not None else None,
+            ws.numel() if ws is not None else 0, torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc)
+    if ov_c is not ov:
+        ov = ov_c.movedim(-1, d)
+        oi = oi_c.movedim(-1, d)
+    return ov, oi

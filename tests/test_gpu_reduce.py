@@ -1,0 +1,270 @@
+"""GPU parity of the reduction kernels against the CPU oracle, through the C ABI.
+
+Every case runs the sm_100a kernel (tensorplay_b200.ops -> ctypes -> libtpb200.so) and the plain-C
+restatement of the reference's CPU kernels (oracle/) on the same seeded input.
+max / min / argmax / argmin: bit-exact.  sum / mean / var / std: within 1e-5 relative of a float64
+evaluation, and in condition-aware agreement with the reference (tests/util.py).
+"""
+import os
+
+import numpy as np
+import pytest
+
+from util import (assert_agrees, assert_bits_equal, assert_close64, assert_index_equal, config1, config3)
+
+pytestmark = pytest.mark.gpu
+
+VALUE_OPS = ["sum", "mean", "var", "std"]
+EXT_OPS = ["max", "min"]
+ARG_OPS = ["argmax", "argmin"]
+
+
+def gpu_view(x, device):
+    """The same strided view of the same bytes, on the GPU."""
+    import torch
+
+    base = x
+    while isinstance(base.base, np.ndarray):
+        base = base.base
+    g = torch.from_numpy(np.ascontiguousarray(base).reshape(-1)).to(device)
+    if not base.flags.c_contiguous:
+        return torch.from_numpy(np.ascontiguousarray(x)).to(device)
+    off = (x.__array_interface__["data"][0] - base.__array_interface__["data"][0]) // 4
+    return torch.as_strided(g, x.shape, [s // 4 for s in x.strides], off)
+
+
+def check(device, x, op, dims=None, keepdim=False, correction=1, what=""):
+    import tensorplay_b200 as tpb
+    from oracle import oracle as O
+
+    xg = gpu_view(x, device)
+    what = f"{what} {op} shape={x.shape} strides={x.strides} dims={dims} keepdim={keepdim} corr={correction}"
+    if op in ARG_OPS:
+        d = None if dims is None else dims[0]
+        got = getattr(tpb, op)(xg, d, keepdim).cpu().numpy()
+        want = O.reduce(op, x, dims, keepdim)
+        assert_index_equal(got, want, what)
+        return
+    if op in EXT_OPS:
+        got = getattr(tpb, op)(xg, dims, keepdim).cpu().numpy()
+        want = O.reduce(op, x, dims, keepdim)
+        assert_bits_equal(got, want, what)
+        return
+    if op in ("var", "std"):
+        got = getattr(tpb, op)(xg, dims, correction, keepdim).cpu().numpy()
+    else:
+        got = getattr(tpb, op)(xg, dims, keepdim).cpu().numpy()
+    truth = O.truth64(op, x, dims, keepdim, correction)
+    ref = O.reduce(op, x, dims, keepdim, correction)
+    assert got.shape == ref.shape, what
+    assert_close64(got, truth, what)
+    if op in ("sum", "mean"):
+        ax = None if dims is None else tuple(d % x.ndim for d in dims)
+        abs_sum = np.abs(x.astype(np.float64)).sum(axis=ax, keepdims=keepdim)
+        if op == "mean":
+            n = x.size if ax is None else int(np.prod([x.shape[a] for a in ax]))
+            abs_sum = abs_sum / max(n, 1)
+        assert_agrees(got, ref, truth, abs_sum, what)
+    else:
+        # var/std: the reference sums the squared deviations sequentially in float32, so its own
+        # distance from float64 grows with the reduction length n (about 1e-4 at n = 3e5)
+        n = x.size if dims is None else int(np.prod([x.shape[d % x.ndim] for d in dims]))
+        assert_close64(ref, truth, what + " (reference vs float64)", rel=max(1e-4, 2e-9 * n))
+
+
+# ------------------------------------------------------------------ known answers ------------
+def test_reference_known_answers(cuda):
+    """The hand-computed cases of the reference's own tests (test/test_reduction.py:35-57,
+    test/test_cuda_reductions.py:19-98)."""
+    import torch
+    import tensorplay_b200 as tpb
+
+    x = torch.tensor([[1.0, 5.0, 2.0], [4.0, 3.0, 6.0]], device=cuda)
+    assert tpb.argmax(x).item() == 5 and tpb.argmin(x).item() == 0
+    assert tpb.argmax(x, 0).tolist() == [1, 0, 1]
+    assert tpb.argmax(x, 1).tolist() == [1, 2]
+    y = torch.tensor([[1.0, 2.0], [3.0, 4.0]], device=cuda)
+    assert tpb.sum(y).item() == 10.0 and tpb.mean(y).item() == 2.5
+    t = torch.ones(3, 4, device=cuda)
+    assert tpb.sum(t, [0]).tolist() == [3.0] * 4
+    assert tpb.sum(t, [1], keepdim=True).shape == (3, 1)
+    assert tpb.mean(t * 2, [0]).tolist() == [2.0] * 4
+    z = torch.tensor([1.0, 2.0, 3.0, 4.0], device=cuda)
+    assert tpb.max(z.reshape(2, 2)).item() == 4.0 and tpb.min(z.reshape(2, 2)).item() == 1.0
+    assert tpb.max(z.reshape(2, 2), [0]).tolist() == [3.0, 4.0]
+    assert abs(tpb.var(z).item() - 5.0 / 3.0) < 1e-6
+    assert abs(tpb.std(z).item() - (5.0 / 3.0) ** 0.5) < 1e-6
+    w = torch.tensor([1.0, 5.0, 2.0, 8.0], device=cuda)
+    assert tpb.argmax(w).item() == 3 and tpb.argmin(w).item() == 0
+
+
+# ------------------------------------------------------------------ small shapes, all dims ---
+SMALL = [((10,), [None, [0]]),
+         ((5, 5), [None, [0], [1], [-1], [0, 1]]),
+         ((2, 3, 4), [None, [0], [1], [2], [0, 2], [1, 2], [0, 1], [0, 1, 2]]),
+         ((3, 4, 5, 6), [[1, 3], [0, 2], [2], [3], [0], [1, 2, 3], [0, 3]]),
+         ((7, 1001), [None, [0], [1]]),
+         ((1, 1), [None, [0], [1]]),
+         ((33, 1, 17), [[0], [1], [2], [0, 2]])]
+
+
+@pytest.mark.parametrize("shape,dimss", SMALL)
+def test_small_shapes(cuda, shape, dimss):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal(shape).astype(np.float32)
+    if x.size > 4:
+        x.flat[3] = x.flat[1]
+    for dims in dimss:
+        for keepdim in (False, True):
+            for op in VALUE_OPS + EXT_OPS:
+                for corr in ((0, 1, 2) if op in ("var", "std") else (1,)):
+                    check(cuda, x, op, dims, keepdim and dims is not None, corr)
+            for op in ARG_OPS:
+                if dims is None or len(dims) == 1:
+                    check(cuda, x, op, dims, keepdim and dims is not None)
+
+
+def test_strided_views(cuda):
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((6, 8, 10)).astype(np.float32)
+    big = rng.standard_normal((40, 67, 131)).astype(np.float32)
+    views = [x.transpose(2, 0, 1), x[:, ::2, 1:9], x.transpose(1, 0, 2)[::2], x[1:, :, 3:],
+             big[:, 1:, 1:], big.transpose(0, 2, 1), big[::3, :, ::2], big.reshape(-1)[5:][::1]]
+    for v in views:
+        dimss = [None] + [[d] for d in range(v.ndim)] + ([[0, v.ndim - 1]] if v.ndim > 1 else [])
+        for dims in dimss:
+            for op in VALUE_OPS + EXT_OPS:
+                check(cuda, v, op, dims)
+            for op in ARG_OPS:
+                if dims is None or len(dims) == 1:
+                    check(cuda, v, op, dims)
+
+
+def test_special_values(cuda):
+    nan, inf = np.float32(np.nan), np.float32(np.inf)
+    rows = [np.array([nan, 1, 3, nan, -0.0, 0.0, 3, -inf], dtype=np.float32),
+            np.array([-0.0, 0.0, -0.0], dtype=np.float32),
+            np.array([0.0, -0.0, 0.0], dtype=np.float32),
+            np.full(5, nan, dtype=np.float32),
+            np.full(700, -inf, dtype=np.float32),
+            np.full(700, inf, dtype=np.float32),
+            np.array([inf, -inf, 1.0], dtype=np.float32)]
+    for r in rows:
+        for op in EXT_OPS + ARG_OPS:
+            check(cuda, r, op, None)
+            check(cuda, r, op, [0])
+        tall = np.tile(r, (300, 1))          # [300, n]: row kernels
+        wide = np.ascontiguousarray(tall.T)  # [n, 300]: column kernel over dim 0
+        for op in EXT_OPS + ARG_OPS:
+            check(cuda, tall, op, [1])
+            check(cuda, wide, op, [0])
+    # sums containing NaN / inf propagate like the reference
+    import tensorplay_b200 as tpb
+    import torch
+    assert np.isnan(tpb.sum(torch.tensor([1.0, float("nan")], device=cuda)).item())
+    assert tpb.sum(torch.tensor([1.0, float("inf")], device=cuda)).item() == float("inf")
+
+
+def test_tie_heavy(cuda):
+    rng = np.random.default_rng(13)
+    x = rng.integers(0, 4, (257, 3001)).astype(np.float32)
+    for op in EXT_OPS + ARG_OPS:
+        check(cuda, x, op, [1])
+        check(cuda, x, op, [0])
+        check(cuda, x, op, None)
+    y = rng.integers(0, 3, (5, 70, 33)).astype(np.float32)
+    for op in EXT_OPS + ARG_OPS:
+        check(cuda, y, op, [1])
+
+
+def test_empty_and_degenerate(cuda):
+    import torch
+    import tensorplay_b200 as tpb
+
+    e = torch.empty(0, device=cuda)
+    assert tpb.sum(e).item() == 0.0
+    assert np.isnan(tpb.mean(e).item())
+    assert np.isnan(tpb.var(e).item())
+    assert tpb.argmax(e).item() == 0
+    with pytest.raises(RuntimeError, match=r"max\(\): Expected reduction dim to be non-empty"):
+        tpb.max(e)
+    with pytest.raises(RuntimeError, match=r"min\(\): Expected reduction dim to be non-empty"):
+        tpb.min(e)
+    z = torch.empty(3, 0, device=cuda)
+    assert tpb.sum(z, [1]).tolist() == [0.0, 0.0, 0.0]
+    assert tpb.max(z, [1]).tolist() == [float("-inf")] * 3     # the reference fills the start value
+    assert tpb.min(z, [1]).tolist() == [float("inf")] * 3
+    assert tpb.sum(z, [0]).shape == (0,)
+    one = torch.tensor([2.0], device=cuda)
+    assert np.isnan(tpb.var(one).item())                         # 0 / max(0, 1-1)
+    assert tpb.var(one, [0], correction=0).item() == 0.0
+    assert tpb.var(torch.tensor([1.0, 3.0], device=cuda), correction=5).item() == float("inf")
+    s = torch.tensor(3.5, device=cuda)                           # 0-dim
+    assert tpb.sum(s).item() == 3.5 and tpb.max(s).item() == 3.5 and tpb.argmax(s).item() == 0
+    with pytest.raises(RuntimeError, match="Dimension out of range"):
+        tpb.sum(torch.ones(2, 2, device=cuda), [2])
+    with pytest.raises(RuntimeError, match="Dimension out of range"):
+        tpb.argmax(torch.ones(2, 2, device=cuda), -3)
+    with pytest.raises(NotImplementedError):
+        tpb.sum(torch.ones(2, dtype=torch.float64, device=cuda))
+    with pytest.raises(RuntimeError):
+        tpb.sum(torch.ones(2))
+
+
+@pytest.mark.parametrize("strategy", ["warp", "cta", "split", "generic"])
+def test_forced_row_strategies(cuda, strategy, monkeypatch):
+    """The same inputs through every row-kernel family (TPB200_FORCE_STRATEGY)."""
+    monkeypatch.setenv("TPB200_FORCE_STRATEGY", strategy)
+    rng = np.random.default_rng(14)
+    x = rng.standard_normal((19, 40007)).astype(np.float32)
+    x[:, 100] = x[:, 7]
+    for op in VALUE_OPS + EXT_OPS + ARG_OPS:
+        check(cuda, x, op, [1], what=strategy)
+        check(cuda, x[:, 1:], op, [1], what=strategy)   # rows not 16-byte aligned
+    flat = rng.standard_normal(1_000_003).astype(np.float32)
+    for op in VALUE_OPS + EXT_OPS + ARG_OPS:
+        check(cuda, flat, op, None, what=strategy)
+
+
+def test_config1_rowwise(cuda):
+    """BASELINE config 1: [4096, 4096] N(0,1), seed 0; sum/mean/var/max/argmax over dim -1."""
+    x = config1()
+    for op in ["sum", "mean", "var", "std", "max", "min", "argmax", "argmin"]:
+        check(cuda, x, op, [-1])
+    import tensorplay_b200 as tpb
+    import torch
+    xg = torch.from_numpy(x).to(cuda)
+    v, i = tpb.max_with_indices(xg, -1)
+    assert torch.equal(v, tpb.max(xg, -1)) and torch.equal(i, tpb.argmax(xg, -1))
+    assert torch.equal(v, xg.gather(1, i[:, None])[:, 0])
+
+
+def test_config3_nonlast(cuda):
+    """BASELINE config 3 at a quarter of its batch ([16, 4096, 512], same generator and seed):
+    sum/mean/max/argmin over dim 1, sum/std over dims (0, 2)."""
+    x = config3(a=16)
+    for op in ["sum", "mean", "max", "min", "argmin", "argmax", "var"]:
+        check(cuda, x, op, [1])
+    for op in ["sum", "std", "mean", "max"]:
+        check(cuda, x, op, [0, 2])
+
+
+def test_whole_tensor_large(cuda):
+    """Whole-tensor reductions with the value distribution of BASELINE config 4 (uniform(-1,1),
+    1% of positions +-1e4) on 2^26+5 elements: the oracle finishes in seconds at this size."""
+    from util import config4
+    x = config4(n=(1 << 26) + 5)
+    for op in ["sum", "mean", "var", "std", "max", "min", "argmax", "argmin"]:
+        check(cuda, x, op, None)
+
+
+def test_run_to_run_bit_identity(cuda):
+    import torch
+    import tensorplay_b200 as tpb
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn(3, 5000, 129, generator=g).to(cuda)
+    for fn, args in [(tpb.sum, ([1],)), (tpb.var, ([0, 2],)), (tpb.sum, (None,)), (tpb.std, (None,)),
+                     (tpb.mean, ([2],))]:
+        a = fn(x, *args).clone()
+        for _ in range(3):
+            assert torch.equal(a.view(torch.int32), fn(x, *args).view(torch.int32))
