@@ -152,6 +152,14 @@ int tpb200_topk_merge(const float* cand_val, const int64_t* cand_idx, int64_t n_
                       int largest, const int64_t* list_offsets, int64_t list_len, float* out_val,
                       int64_t* out_idx, void* stream);
 
+/* ---- diagnostics ------------------------------------------------------------------------------
+ * Every device-side wait in these kernels (on a bulk copy into shared memory) is bounded; a kernel
+ * whose wait gave up leaves its outputs unwritten and sets a per-device status word.  This call
+ * SYNCHRONISES with the device, returns the word in *status_out (0 = no wait ever gave up) and
+ * clears it.  No reference counterpart.
+ */
+int tpb200_device_status(int* status_out);
+
 #ifdef __cplusplus
 }
 #endif

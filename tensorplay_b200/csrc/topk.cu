@@ -21,12 +21,15 @@
 #include "host_util.h"
 
 #include <algorithm>
+#include <mutex>
+#include <string>
 
 namespace tpb {
 
-constexpr int kTopkThreads = 512;
-constexpr int kTileVecs = 4;                                  // float4 loads per thread per tile
-constexpr int kTile = kTopkThreads * kTileVecs * 4;           // 8192 elements
+constexpr int kStreamThreads = 256;
+constexpr int kTile = kStreamThreads * 16;                    // 4096 elements = one 16 KB stage
+constexpr int kStages = 4;                                    // shared-memory ring depth
+constexpr int kSortThreads = 512;
 constexpr int kMaxStreamK = 2048;                             // largest k of the streaming path
 constexpr int kMaxSortRow = 16384;                            // longest row sorted whole in smem
 constexpr int kMaxMergeCand = 8192;                           // tpb200_topk_merge limit
@@ -79,7 +82,7 @@ struct TopkGeom {
     long long chunk;      // slice length per CTA
     int S;                // slices per row
     int B;                // candidate buffer capacity (power of two)
-    int gpt;              // bootstrap groups per thread (1, 2 or 4)
+    int soft;             // buffer fill that triggers a cut at the next tile boundary
 };
 
 __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom& g, long long r) {
@@ -89,29 +92,31 @@ __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom
 }
 
 // ------------------------------------------------------------------ streaming kernel -------
+// Shared-memory ring: kStages tiles of kTile floats, filled by cp.async.bulk (one elected thread
+// issues, an mbarrier per stage counts the bytes), consumed by all 256 threads.  The CTA-wide
+// barrier that ends every tile also tells the issuing thread that the stage may be refilled, so
+// up to (kStages-1) x 16 KB are in flight per CTA while a tile is being compared.
 struct StreamShared {
-    int cnt;
+    unsigned long long full[kStages];
     unsigned long long tau;
+    int cnt;
+    int err;
 };
 
 template <bool LARGEST>
 __device__ __forceinline__ float worst_value() { return LARGEST ? -INFINITY : INFINITY; }
 
-// Load this thread's 16 elements of tile t of the slice; absent ones get the worst value.
-template <bool LARGEST, bool VEC>
-__device__ __forceinline__ void load_tile(float (&x)[16], const float* slice, long long es,
-                                          long long len, long long tile_off, int tid) {
+// Register path for rows that cannot use bulk copies (element stride != 1, or not 16-byte
+// aligned): this thread's 16 elements of the tile; absent ones get the worst value.
+template <bool LARGEST>
+__device__ __forceinline__ void load_tile_direct(float (&x)[16], const float* slice, long long es,
+                                                 long long len, long long tile_off, int tid) {
 #pragma unroll
-    for (int u = 0; u < kTileVecs; ++u) {
-        long long e0 = tile_off + ((long long)u * kTopkThreads + tid) * 4;
-        if (VEC && e0 + 3 < len) {
-            float4 v = ld_stream4(slice + e0);
-            x[4 * u] = v.x; x[4 * u + 1] = v.y; x[4 * u + 2] = v.z; x[4 * u + 3] = v.w;
-        } else {
+    for (int u = 0; u < 4; ++u) {
+        long long e0 = tile_off + ((long long)u * kStreamThreads + tid) * 4;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                x[4 * u + c] = (e0 + c < len) ? ld_stream1(slice + (e0 + c) * es) : worst_value<LARGEST>();
-        }
+        for (int c = 0; c < 4; ++c)
+            x[4 * u + c] = (e0 + c < len) ? ld_stream1(slice + (e0 + c) * es) : worst_value<LARGEST>();
     }
 }
 
@@ -132,11 +137,14 @@ __device__ void compact(unsigned long long* buf, StreamShared* sh, int B, int k,
     __syncthreads();
 }
 
-template <bool LARGEST, bool VEC>
-__global__ void __launch_bounds__(kTopkThreads, 2)
+template <bool LARGEST, bool BULK>
+__global__ void __launch_bounds__(kStreamThreads, 3)
 topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
-                   float* __restrict__ out_val, long long* __restrict__ out_idx) {
-    extern __shared__ __align__(16) unsigned long long buf[];
+                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float* ring = reinterpret_cast<float*>(smem_raw);
+    unsigned long long* buf =
+        reinterpret_cast<unsigned long long*>(smem_raw + (BULK ? (size_t)kStages * kTile * sizeof(float) : 0));
     __shared__ StreamShared sh;
     const int tid = threadIdx.x, lane = tid & 31;
     const int s = blockIdx.x;
@@ -147,13 +155,35 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     if (len > g.chunk) len = g.chunk;
     const float* slice = row + begin * g.es;
     const int ntiles = (int)((len + kTile - 1) / kTile);
-    const int B = g.B, k = (int)g.k;
+    const int B = g.B, k = (int)g.k, soft_limit = g.soft;
 
-    if (tid == 0) { sh.cnt = 0; sh.tau = 0ull; }
+    // thread 0: start the copy of tile u into its stage (a ragged tail of < 4 floats by hand)
+    auto issue = [&](int u) {
+        const int st = u % kStages;
+        const long long off = (long long)u * kTile;
+        long long n = len - off;
+        if (n > kTile) n = kTile;
+        const int n4 = (int)(n & ~3LL);
+        float* dst = ring + (size_t)st * kTile;
+        for (int i = n4; i < (int)n; ++i) dst[i] = ld_stream1(slice + off + i);
+        if (n4 > 0) {
+            mbar_arrive_expect_tx(&sh.full[st], (unsigned)n4 * 4u);
+            bulk_g2s(dst, slice + off, (unsigned)n4 * 4u, &sh.full[st]);
+        } else {
+            mbar_arrive(&sh.full[st]);
+        }
+    };
+
+    if (tid == 0) {
+        sh.cnt = 0; sh.tau = 0ull; sh.err = 0;
+        if (BULK) {
+            for (int i = 0; i < kStages; ++i) mbar_init(&sh.full[i], 1);
+            fence_mbar_init();
+        }
+    }
     __syncthreads();
-
-    float x[16], nx[16];
-    load_tile<LARGEST, VEC>(x, slice, g.es, len, 0, tid);
+    if (BULK && tid == 0)
+        for (int u = 0; u < kStages && u < ntiles; ++u) issue(u);
 
     unsigned long long tau = 0ull;  // exclusive: candidate iff word > tau
     float tvf = worst_value<LARGEST>();
@@ -161,20 +191,34 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
 
     for (int t = 0; t < ntiles; ++t) {
         const long long tile_off = (long long)t * kTile;
-        if (t + 1 < ntiles) load_tile<LARGEST, VEC>(nx, slice, g.es, len, tile_off + kTile, tid);
+        float x[16];
+        bool timeout = false;
+        if (BULK) {
+            const int st = t % kStages;
+            timeout = !mbar_wait_bounded(&sh.full[st], (unsigned)((t / kStages) & 1));
+            const float4* src = reinterpret_cast<const float4*>(ring + (size_t)st * kTile);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                float4 v = src[u * kStreamThreads + tid];
+                x[4 * u] = v.x; x[4 * u + 1] = v.y; x[4 * u + 2] = v.z; x[4 * u + 3] = v.w;
+            }
+        } else {
+            load_tile_direct<LARGEST>(x, slice, g.es, len, tile_off, tid);
+        }
 
-        // position of x[4u+c] in the row: begin + tile_off + (u*512 + tid)*4 + c
+        // position of x[4u+c] in the row: begin + tile_off + (u*256 + tid)*4 + c
         unsigned valid = 0xffffu;
         if (tile_off + kTile > len) {
             valid = 0u;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                long long e = tile_off + ((long long)(j >> 2) * kTopkThreads + tid) * 4 + (j & 3);
+                long long e = tile_off + ((long long)(j >> 2) * kStreamThreads + tid) * 4 + (j & 3);
                 if (e < len) valid |= 1u << j;
+                else x[j] = worst_value<LARGEST>();
             }
         }
         auto idx_of = [&](int j) -> unsigned {
-            return (unsigned)(begin + tile_off + ((long long)(j >> 2) * kTopkThreads + tid) * 4 + (j & 3));
+            return (unsigned)(begin + tile_off + ((long long)(j >> 2) * kStreamThreads + tid) * 4 + (j & 3));
         };
 
         unsigned m = 0u;
@@ -184,22 +228,17 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
                 bool p = LARGEST ? (x[j] > tvf) : (x[j] < tvf);
                 m |= p ? (1u << j) : 0u;
             }
-        } else if (mode == 0 && t == 0 && len >= kTile && k <= kTopkThreads * g.gpt) {
-            // bootstrap: k-th largest of the per-thread group maxima bounds the k-th best from below
-            const int gpt = g.gpt, per = 16 / gpt;
-            for (int gi = 0; gi < gpt; ++gi) {
-                unsigned long long gm = 0ull;
+        } else if (mode == 0 && t == 0 && len >= kTile && k <= kStreamThreads) {
+            // bootstrap: the k-th largest of the 256 per-thread maxima bounds the k-th best from below
+            unsigned long long gm = 0ull;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (j / per == gi) {
-                        unsigned long long w = rank_word<LARGEST>(x[j], idx_of(j));
-                        gm = w > gm ? w : gm;
-                    }
-                }
-                buf[gi * kTopkThreads + tid] = gm;
+            for (int j = 0; j < 16; ++j) {
+                unsigned long long w = rank_word<LARGEST>(x[j], idx_of(j));
+                gm = w > gm ? w : gm;
             }
+            buf[tid] = gm;
             __syncthreads();
-            bitonic_desc(buf, kTopkThreads * gpt, tid, kTopkThreads);
+            bitonic_desc(buf, kStreamThreads, tid, kStreamThreads);
             tau = buf[k - 1] - 1ull;
             __syncthreads();
 #pragma unroll
@@ -219,41 +258,52 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
             m &= valid;
         }
 
-        if (__syncthreads_or(m != 0u)) {
-            unsigned pending = m;
-            while (true) {
-                // reserve buffer slots: exclusive scan inside the warp, one atomic per warp
-                int n = __popc(pending);
-                int incl = n;
+        // optimistic append: slots are reserved with one atomic per warp; what does not fit stays
+        // pending and forces a cut of the buffer below
+        unsigned pending = m;
+        auto try_append = [&]() {
+            int n = __popc(pending);
+            int incl = n;
 #pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    int o = __shfl_up_sync(kFull, incl, d);
-                    if (lane >= d) incl += o;
-                }
-                int total = __shfl_sync(kFull, incl, 31);
-                int base = 0;
-                if (total > 0) {
-                    if (lane == 31) base = atomicAdd(&sh.cnt, total);
-                    base = __shfl_sync(kFull, base, 31);
-                }
-                int pos = base + incl - n;
-                bool over = false;
-                if (pending) {
+            for (int d = 1; d < 32; d <<= 1) {
+                int o = __shfl_up_sync(kFull, incl, d);
+                if (lane >= d) incl += o;
+            }
+            int total = __shfl_sync(kFull, incl, 31);
+            int base = 0;
+            if (lane == 31) base = atomicAdd(&sh.cnt, total);
+            base = __shfl_sync(kFull, base, 31);
+            int pos = base + incl - n;
+            if (pending) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (pending & (1u << j)) {
-                            if (pos < B) {
-                                buf[pos] = rank_word<LARGEST>(x[j], idx_of(j));
-                                pending &= ~(1u << j);
-                            } else {
-                                over = true;
-                            }
-                            ++pos;
+                for (int j = 0; j < 16; ++j) {
+                    if (pending & (1u << j)) {
+                        if (pos < B) {
+                            buf[pos] = rank_word<LARGEST>(x[j], idx_of(j));
+                            pending &= ~(1u << j);
                         }
+                        ++pos;
                     }
                 }
-                if (!__syncthreads_or(over)) break;
-                compact(buf, &sh, B, k, tid, kTopkThreads);
+            }
+        };
+        if (__any_sync(kFull, pending != 0u)) try_append();
+
+        const bool soft = tid == 0 && *(volatile int*)&sh.cnt > soft_limit;
+        if (__syncthreads_or((pending != 0u) | soft | timeout)) {
+            if (timeout) sh.err = 1;
+            __syncthreads();
+            if (sh.err) {
+                // a copy never landed: give the copies still in flight a bounded chance to finish,
+                // flag the failure for the host, and leave without touching the outputs
+                if (BULK)
+                    for (int u = t; u < ntiles && u < t + kStages; ++u)
+                        mbar_wait_bounded(&sh.full[u % kStages], (unsigned)((u / kStages) & 1));
+                if (tid == 0 && status) atomicExch(status, 1);
+                return;
+            }
+            while (true) {
+                compact(buf, &sh, B, k, tid, kStreamThreads);
                 tau = sh.tau;
                 if (pending) {
 #pragma unroll
@@ -261,23 +311,25 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
                         if ((pending & (1u << j)) && !(rank_word<LARGEST>(x[j], idx_of(j)) > tau))
                             pending &= ~(1u << j);
                 }
-                mode = tau == 0ull ? 0 : ((tau >> 32) == 0ull ? 2 : 1);
-                tvf = key_value<LARGEST>((unsigned)(tau >> 32));
+                if (__any_sync(kFull, pending != 0u)) try_append();
+                if (!__syncthreads_or(pending != 0u)) break;
             }
+            mode = tau == 0ull ? 0 : ((tau >> 32) == 0ull ? 2 : 1);
+            tvf = key_value<LARGEST>((unsigned)(tau >> 32));
         }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) x[j] = nx[j];
+        // every thread has its tile in registers: the stage can take tile t + kStages
+        if (BULK && tid == 0 && t + kStages < ntiles) issue(t + kStages);
     }
 
     // final cut: the slice's best min(cnt, k), sorted
     __syncthreads();
-    compact(buf, &sh, B, k, tid, kTopkThreads);
+    compact(buf, &sh, B, k, tid, kStreamThreads);
     const int cnt = sh.cnt;
     if (ws) {
         unsigned long long* dst = ws + ((size_t)r * g.S + s) * (size_t)k;
-        for (int j = tid; j < k; j += kTopkThreads) dst[j] = j < cnt ? buf[j] : 0ull;
+        for (int j = tid; j < k; j += kStreamThreads) dst[j] = j < cnt ? buf[j] : 0ull;
     } else {
-        for (int j = tid; j < k && j < cnt; j += kTopkThreads) {
+        for (int j = tid; j < k && j < cnt; j += kStreamThreads) {
             unsigned idx = word_index(buf[j]);
             out_idx[r * k + j] = (long long)idx;
             out_val[r * k + j] = row[(long long)idx * g.es];
@@ -289,7 +341,7 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
 // FROM_ROW: rank every element of a short row.  Otherwise: merge the S*k slice survivors of a row.
 // One CTA per row, whole working set in shared memory.
 template <bool LARGEST, bool FROM_ROW>
-__global__ void __launch_bounds__(kTopkThreads)
+__global__ void __launch_bounds__(kSortThreads)
 topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long long* __restrict__ ws,
                  int n_items, int N, float* __restrict__ out_val, long long* __restrict__ out_idx) {
     extern __shared__ __align__(16) unsigned long long buf[];
@@ -316,7 +368,7 @@ topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long l
 // ------------------------------------------------------------------ global merge -----------
 // Candidates carry 64-bit tensor-global indices, so the order is on (key, index) pairs.
 template <bool LARGEST>
-__global__ void __launch_bounds__(kTopkThreads)
+__global__ void __launch_bounds__(kSortThreads)
 topk_merge_pairs_kernel(const float* __restrict__ cv, const long long* __restrict__ ci, int n, int N,
                         int k, const long long* __restrict__ list_off, int list_len,
                         float* __restrict__ out_val, long long* __restrict__ out_idx) {
@@ -359,6 +411,25 @@ topk_merge_pairs_kernel(const float* __restrict__ cv, const long long* __restric
         out_idx[j] = sidx[j];
         out_val[j] = cv[sslot[j]];
     }
+}
+
+// ------------------------------------------------------------------ device status ----------
+// Set to 1 by a kernel whose bounded wait on a bulk copy gave up (its outputs are then not
+// written).  One word per device, lives in the module's global memory.
+__device__ int g_device_status = 0;
+
+static int* device_status_word() {
+    static std::mutex mu;
+    static int* cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return nullptr; }
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cached[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+        cached[dev] = (int*)p;
+    }
+    return cached[dev];
 }
 
 // ------------------------------------------------------------------ planner ----------------
@@ -443,12 +514,12 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
         return fail(TPB200_ERR_UNSUPPORTED, "more than 65535 rows of more than 4096 elements are not supported");
     }
     pl->path = TK_STREAM;
-    g.B = pow2_ceil(std::max<long long>(2 * k, 1024));
-    g.gpt = k <= kTopkThreads ? 1 : (k <= 2 * kTopkThreads ? 2 : 4);
-    // slices: enough CTAs to fill the GPU, each slice at least two tiles and at least 4k long
+    g.B = pow2_ceil(std::max<long long>(4 * k, 1024));
+    g.soft = (int)std::max<long long>(2 * k, 256);
+    // slices: enough CTAs to fill the GPU, each slice at least eight tiles and at least 8k long
     const int sms = sm_count();
-    long long want = ceil_div((long long)sms * 6, rows);
-    long long most = std::max(1LL, len / std::max<long long>(2 * kTile, 4 * k));
+    long long want = ceil_div((long long)sms * 4, rows);
+    long long most = std::max(1LL, len / std::max<long long>(8 * kTile, 8 * k));
     long long cap = std::max(1LL, (long long)kMaxSortRow / k);
     long long S = std::max(1LL, std::min(std::min(want, most), cap));
     const char* fs = getenv("TPB200_TOPK_SLICES");
@@ -478,23 +549,32 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
         size_t sm = (size_t)pl.N * 8;
         int rc = allow_smem(topk_sort_kernel<LARGEST, true>, sm);
         if (rc) return rc;
-        int threads = std::min(kTopkThreads, std::max(32, pl.N / 2));
+        int threads = std::min(kSortThreads, std::max(32, pl.N / 2));
         if (g.rows > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
         topk_sort_kernel<LARGEST, true><<<(unsigned)g.rows, threads, sm, st>>>(in, g, nullptr, (int)g.len, pl.N, ov, oi);
         TPB_LAUNCH_OK("topk_sort_kernel");
         return TPB200_OK;
     }
-    size_t sm = (size_t)g.B * 8;
     dim3 grid((unsigned)g.S, (unsigned)g.rows);
     unsigned long long* w = g.S > 1 ? (unsigned long long*)ws : nullptr;
-    if (pl.vec) topk_stream_kernel<LARGEST, true><<<grid, kTopkThreads, sm, st>>>(in, g, w, ov, oi);
-    else topk_stream_kernel<LARGEST, false><<<grid, kTopkThreads, sm, st>>>(in, g, w, ov, oi);
+    int* status = device_status_word();
+    if (pl.vec) {
+        size_t sm = (size_t)g.B * 8 + (size_t)kStages * kTile * sizeof(float);
+        int rc = allow_smem(topk_stream_kernel<LARGEST, true>, sm);
+        if (rc) return rc;
+        topk_stream_kernel<LARGEST, true><<<grid, kStreamThreads, sm, st>>>(in, g, w, ov, oi, status);
+    } else {
+        size_t sm = (size_t)g.B * 8;
+        int rc = allow_smem(topk_stream_kernel<LARGEST, false>, sm);
+        if (rc) return rc;
+        topk_stream_kernel<LARGEST, false><<<grid, kStreamThreads, sm, st>>>(in, g, w, ov, oi, status);
+    }
     TPB_LAUNCH_OK("topk_stream_kernel");
     if (g.S > 1) {
         size_t msm = (size_t)pl.mergeN * 8;
         int rc = allow_smem(topk_sort_kernel<LARGEST, false>, msm);
         if (rc) return rc;
-        int threads = std::min(kTopkThreads, std::max(32, pl.mergeN / 2));
+        int threads = std::min(kSortThreads, std::max(32, pl.mergeN / 2));
         topk_sort_kernel<LARGEST, false><<<(unsigned)g.rows, threads, msm, st>>>(in, g, w, g.S * (int)g.k, pl.mergeN, ov, oi);
         TPB_LAUNCH_OK("topk_sort_kernel(merge)");
     }
@@ -550,7 +630,7 @@ extern "C" int tpb200_topk_merge(const float* cand_val, const int64_t* cand_idx,
     const int N = std::max(2, pow2_ceil(n_cand));
     const size_t sm = (size_t)N * (8 + 4 + 4);
     cudaStream_t st = (cudaStream_t)stream;
-    const int threads = std::min(kTopkThreads, std::max(32, N / 2));
+    const int threads = std::min(kSortThreads, std::max(32, N / 2));
     if (largest) {
         int rc = allow_smem(topk_merge_pairs_kernel<true>, sm);
         if (rc) return rc;
@@ -561,5 +641,14 @@ extern "C" int tpb200_topk_merge(const float* cand_val, const int64_t* cand_idx,
         topk_merge_pairs_kernel<false><<<1, threads, sm, st>>>(cand_val, (const long long*)cand_idx, (int)n_cand, N, (int)k, lo, ll, out_val, (long long*)out_idx);
     }
     TPB_LAUNCH_OK("topk_merge_pairs_kernel");
+    return TPB200_OK;
+}
+
+extern "C" int tpb200_device_status(int* status_out) {
+    if (!status_out) return fail(TPB200_ERR_INVALID, "status_out is NULL");
+    int v = 0, zero = 0;
+    TPB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
+    if (v != 0) TPB_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+    *status_out = v;
     return TPB200_OK;
 }

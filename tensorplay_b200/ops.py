@@ -62,10 +62,8 @@ def _dims_mask(x: torch.Tensor, dim) -> tuple[int, list[int]]:
     for d in dims:
         d = int(d)
         dd = d + nd if d < 0 else d
-        if dd < 0 or dd >= _py.max(nd, 1):
+        if dd < 0 or dd >= nd:   # a 0-dim tensor has no valid dim, as in the reference
             raise RuntimeError("Dimension out of range")
-        if nd == 0:
-            continue
         mask |= 1 << dd
         if dd not in out:
             out.append(dd)
@@ -83,7 +81,12 @@ def _out_shape(x: torch.Tensor, dims: list[int], keepdim: bool) -> list[int]:
     return shape
 
 
-def _reduce(op: str, x: torch.Tensor, dim, keepdim: bool, correction: int = 1, index_dim: int = -1):
+def _check_out(t, shape, dtype, device, what):
+    if tuple(t.shape) != tuple(shape) or t.dtype != dtype or t.device != device or not t.is_contiguous():
+        raise ValueError(f"{what}: out must be a contiguous {dtype} tensor of shape {tuple(shape)} on {device}")
+
+
+def _reduce(op: str, x: torch.Tensor, dim, keepdim: bool, correction: int = 1, index_dim: int = -1, out=None):
     _check_input(x, op)
     mask, dims = _dims_mask(x, dim)
     L = _lib.lib()
@@ -94,8 +97,17 @@ def _reduce(op: str, x: torch.Tensor, dim, keepdim: bool, correction: int = 1, i
     want_val = op not in ("argmax", "argmin")
     want_idx = op in ("argmax", "argmin", "max_argmax", "min_argmin")
     with torch.cuda.device(x.device):
-        ov = torch.empty(shape, dtype=torch.float32, device=x.device) if want_val else None
-        oi = torch.empty(shape, dtype=torch.int64, device=x.device) if want_idx else None
+        if out is not None:
+            outs = list(out) if isinstance(out, (tuple, list)) else [out]
+            ov = outs.pop(0) if want_val else None
+            oi = outs.pop(0) if want_idx else None
+            if ov is not None:
+                _check_out(ov, shape, torch.float32, x.device, op)
+            if oi is not None:
+                _check_out(oi, shape, torch.int64, x.device, op)
+        else:
+            ov = torch.empty(shape, dtype=torch.float32, device=x.device) if want_val else None
+            oi = torch.empty(shape, dtype=torch.int64, device=x.device) if want_idx else None
         nbytes = L.tpb200_reduce_workspace_bytes(_lib.OP[op], _lib.F32, nd, sizes, strides, mask)
         ws = _workspace(x.device, nbytes)
         rc = L.tpb200_reduce(
@@ -114,66 +126,65 @@ def _check_dtype(dtype, what):
         raise NotImplementedError(f"{what}: only dtype=float32 (or None) is supported")
 
 
-def sum(x, dim=None, keepdim=False, *, dtype=None):
+def sum(x, dim=None, keepdim=False, *, dtype=None, out=None):
     _check_dtype(dtype, "sum")
-    return _reduce("sum", x, dim, keepdim)
+    return _reduce("sum", x, dim, keepdim, out=out)
 
 
-def mean(x, dim=None, keepdim=False, *, dtype=None):
+def mean(x, dim=None, keepdim=False, *, dtype=None, out=None):
     _check_dtype(dtype, "mean")
-    return _reduce("mean", x, dim, keepdim)
+    return _reduce("mean", x, dim, keepdim, out=out)
 
 
-def var(x, dim=None, correction=1, keepdim=False):
-    return _reduce("var", x, dim, keepdim, correction)
+def var(x, dim=None, correction=1, keepdim=False, *, out=None):
+    return _reduce("var", x, dim, keepdim, correction, out=out)
 
 
-def std(x, dim=None, correction=1, keepdim=False):
-    return _reduce("std", x, dim, keepdim, correction)
+def std(x, dim=None, correction=1, keepdim=False, *, out=None):
+    return _reduce("std", x, dim, keepdim, correction, out=out)
 
 
-def max(x, dim=None, keepdim=False):
-    return _reduce("max", x, dim, keepdim)
+def max(x, dim=None, keepdim=False, *, out=None):
+    return _reduce("max", x, dim, keepdim, out=out)
 
 
-def min(x, dim=None, keepdim=False):
-    return _reduce("min", x, dim, keepdim)
+def min(x, dim=None, keepdim=False, *, out=None):
+    return _reduce("min", x, dim, keepdim, out=out)
 
 
-def _arg(op, x, dim, keepdim):
+def _arg(op, x, dim, keepdim, out=None):
     if dim is None:
-        return _reduce(op, x, None, False, index_dim=-1)
+        return _reduce(op, x, None, False, index_dim=-1, out=out)
     if not isinstance(dim, int):
         raise TypeError(f"{op}(): dim must be an int or None")
     nd = x.dim()
     d = dim + nd if dim < 0 else dim
-    if d < 0 or d >= _py.max(nd, 1):
+    if d < 0 or d >= nd:
         raise RuntimeError("Dimension out of range")
-    if nd == 0:
-        return _reduce(op, x, None, False, index_dim=-1)
-    return _reduce(op, x, d, keepdim, index_dim=d)
+    return _reduce(op, x, d, keepdim, index_dim=d, out=out)
 
 
-def argmax(x, dim=None, keepdim=False):
-    return _arg("argmax", x, dim, keepdim)
+def argmax(x, dim=None, keepdim=False, *, out=None):
+    return _arg("argmax", x, dim, keepdim, out)
 
 
-def argmin(x, dim=None, keepdim=False):
-    return _arg("argmin", x, dim, keepdim)
+def argmin(x, dim=None, keepdim=False, *, out=None):
+    return _arg("argmin", x, dim, keepdim, out)
 
 
-def max_with_indices(x, dim, keepdim=False):
+def max_with_indices(x, dim, keepdim=False, *, out=None):
     """(max.dim values, argmax indices) from one pass over the input."""
-    return _arg("max_argmax", x, dim, keepdim)
+    return _arg("max_argmax", x, dim, keepdim, out)
 
 
-def min_with_indices(x, dim, keepdim=False):
-    return _arg("min_argmin", x, dim, keepdim)
+def min_with_indices(x, dim, keepdim=False, *, out=None):
+    return _arg("min_argmin", x, dim, keepdim, out)
 
 
-def topk(x, k, dim=-1, largest=True, sorted=True):
+def topk(x, k, dim=-1, largest=True, sorted=True, *, out=None):
     """First k entries of each row along `dim`, stably sorted by value (descending if largest),
-    ties in ascending index.  Returns (values float32, indices int64)."""
+    ties in ascending index.  Returns (values float32, indices int64).  `out=(values, indices)`
+    (contiguous, only for dim = last) makes the call allocation-free."""
     _check_input(x, "topk")
     nd = x.dim()
     d = dim + nd if dim < 0 else dim
@@ -186,8 +197,15 @@ def topk(x, k, dim=-1, largest=True, sorted=True):
     if nd:
         shape[d] = int(k)
     with torch.cuda.device(x.device):
-        ov = torch.empty(shape, dtype=torch.float32, device=x.device)
-        oi = torch.empty(shape, dtype=torch.int64, device=x.device)
+        if out is not None:
+            if nd and d != nd - 1:
+                raise ValueError("topk: out= is only supported for dim = last")
+            ov, oi = out
+            _check_out(ov, shape, torch.float32, x.device, "topk")
+            _check_out(oi, shape, torch.int64, x.device, "topk")
+        else:
+            ov = torch.empty(shape, dtype=torch.float32, device=x.device)
+            oi = torch.empty(shape, dtype=torch.int64, device=x.device)
         nbytes = L.tpb200_topk_workspace_bytes(_lib.F32, nd, sizes, strides, d, int(k))
         ws = _workspace(x.device, nbytes)
         # outputs are written as [rows..., k] with k innermost; move k back to `dim` afterwards

@@ -1,0 +1,158 @@
+"""GPU tests of the sharded paths.  The per-rank kernels never wait on one another, so G ranks are
+emulated on one GPU by running them one after the other into the slots of the gather buffer; with
+two or more GPUs the real one-process-per-GPU path over NCCL is run as well."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from util import assert_close64, config4
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.parametrize("G", [1, 2, 4, 8])
+def test_whole_tensor_partials_and_rank_ordered_combine(cuda, G):
+    import torch
+    import tensorplay_b200 as tpb
+    from tensorplay_b200 import _lib
+    from oracle import oracle as O
+
+    n = (1 << 24) + 1237
+    x = config4(n=n)
+    x[n // 2] = 3e4
+    x[n // 2 + G * 1000 + 1] = 3e4         # tie in a later partition: the lower global index must win
+    xg = torch.from_numpy(x).to(cuda)
+    L = _lib.lib()
+    records = torch.zeros(G, _lib.PARTIAL_BYTES, dtype=torch.uint8, device=cuda)
+    st = torch.cuda.current_stream().cuda_stream
+    for fam, ops in [("sum", ["sum", "mean"]), ("var", ["var", "std"]),
+                     ("max_argmax", ["max", "argmax", "max_argmax"]), ("min_argmin", ["min", "argmin"])]:
+        for g in range(G):
+            a, b = tpb.flat_partition(n, g, G)
+            part = xg[a:b]
+            nb = L.tpb200_reduce_partial_workspace_bytes(_lib.OP[fam], 0, b - a)
+            ws = torch.empty(max(nb, 8), dtype=torch.uint8, device=cuda)
+            _lib.check(L.tpb200_reduce_partial(_lib.OP[fam], part.data_ptr(), 0, b - a, a, records[g].data_ptr(),
+                                               ws.data_ptr(), ws.numel(), st))
+        for op in ops:
+            ov = torch.empty(1, device=cuda)
+            oi = torch.empty(1, dtype=torch.int64, device=cuda)
+            want_val = op not in ("argmax", "argmin")
+            want_idx = op in ("argmax", "argmin", "max_argmax")
+            _lib.check(L.tpb200_reduce_combine(_lib.OP[op], records.data_ptr(), G, n, 1,
+                                               ov.data_ptr() if want_val else None,
+                                               oi.data_ptr() if want_idx else None, st))
+            if op in ("sum", "mean", "var", "std"):
+                assert_close64(ov.cpu().numpy()[0], O.truth64(op, x), f"G={G} {op}")
+            else:
+                base = op.replace("_argmax", "")
+                if want_val:
+                    assert ov.item() == float(O.reduce("max" if "max" in op else "min", x))
+                if want_idx:
+                    assert oi.item() == int(O.reduce("argmax" if "max" in op else "argmin", x)), (G, op)
+
+
+@pytest.mark.parametrize("G", [1, 2, 8])
+def test_global_topk_merge(cuda, G):
+    import torch
+    import tensorplay_b200 as tpb
+    from tensorplay_b200 import _lib
+    from oracle import oracle as O
+
+    rng = np.random.default_rng(31)
+    n = 400000
+    x = rng.integers(0, 500, n).astype(np.float32)       # tie-heavy: global index order decides
+    xg = torch.from_numpy(x).to(cuda)
+    L = _lib.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    for k, largest in [(64, True), (64, False), (1024, True)]:
+        if G * k > 8192:
+            continue
+        cv = torch.empty(G, k, device=cuda)
+        ci = torch.empty(G, k, dtype=torch.int64, device=cuda)
+        offs = torch.empty(G, dtype=torch.int64, device=cuda)
+        for g in range(G):
+            a, b = tpb.flat_partition(n, g, G)
+            v, i = tpb.topk(xg[a:b], k, 0, largest)
+            cv[g], ci[g] = v, i
+            offs[g] = a
+        ov = torch.empty(k, device=cuda)
+        oi = torch.empty(k, dtype=torch.int64, device=cuda)
+        _lib.check(L.tpb200_topk_merge(cv.data_ptr(), ci.data_ptr(), G * k, k, int(largest), offs.data_ptr(), k,
+                                       ov.data_ptr(), oi.data_ptr(), st))
+        wv, wi = O.topk(x[None, :], k, -1, largest)
+        assert np.array_equal(oi.cpu().numpy(), wi[0]), (G, k, largest)
+        assert np.array_equal(ov.cpu().numpy().view(np.uint32), wv[0].view(np.uint32))
+
+
+def test_sharded_reducer_one_rank(cuda):
+    import torch
+    import tensorplay_b200 as tpb
+    x = torch.arange(1 << 20, dtype=torch.float32, device=cuda)
+    red = tpb.ShardedReducer(cuda)
+    v, i = red.reduce("max_argmax", x, 0, x.numel())
+    assert v.item() == float((1 << 20) - 1) and i.item() == (1 << 20) - 1
+    v, _ = red.reduce("mean", x, 0, x.numel())
+    assert abs(v.item() - ((1 << 20) - 1) / 2) <= 1e-5 * ((1 << 20) - 1) / 2
+    tv, ti = red.topk(x, 8, 0, True)
+    assert ti.tolist() == list(range((1 << 20) - 1, (1 << 20) - 9, -1))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _nccl_worker(rank, world, port, ret):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(HERE))
+    sys.path.insert(0, HERE)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import tensorplay_b200 as tpb
+        from util import config4
+        n = (1 << 22) + 11
+        x = config4(n=n)
+        a, b = tpb.flat_partition(n, rank, world)
+        local = torch.from_numpy(x[a:b].copy()).to(dev)
+        red = tpb.ShardedReducer(dev)
+        out = {}
+        for op in ("sum", "var", "max_argmax", "argmin"):
+            v, i = red.reduce(op, local, a, n)
+            out[op] = (None if v is None else float(v.item()), None if i is None else int(i.item()))
+        tv, ti = red.topk(local, 32, a, True)
+        out["topk"] = ti.tolist()
+        ret[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_over_nccl(cuda):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from oracle import oracle as O
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_nccl_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret[0] == ret[1]
+    n = (1 << 22) + 11
+    x = config4(n=n)
+    assert_close64(np.float32(ret[0]["sum"][0]), O.truth64("sum", x), "nccl sum")
+    assert_close64(np.float32(ret[0]["var"][0]), O.truth64("var", x), "nccl var")
+    assert ret[0]["max_argmax"][1] == int(O.reduce("argmax", x))
+    assert ret[0]["argmin"][1] == int(O.reduce("argmin", x))
+    assert ret[0]["topk"] == O.topk(x[None, :], 32, -1, True)[1][0].tolist()
