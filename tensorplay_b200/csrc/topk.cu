@@ -27,8 +27,9 @@
 namespace tpb {
 
 constexpr int kStreamThreads = 256;
-constexpr int kTile = kStreamThreads * 16;                    // 4096 elements = one 16 KB stage
-constexpr int kStages = 4;                                    // shared-memory ring depth
+constexpr int kStreamWarps = kStreamThreads / 32;
+constexpr int kWarpTile = 32 * 32;                            // 1024 elements per warp and iteration
+constexpr int kTile = kStreamWarps * kWarpTile;               // elements all warps consume per round
 constexpr int kSortThreads = 512;
 constexpr int kMaxStreamK = 2048;                             // largest k of the streaming path
 constexpr int kMaxSortRow = 16384;                            // longest row sorted whole in smem
@@ -92,44 +93,159 @@ __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom
 }
 
 // ------------------------------------------------------------------ streaming kernel -------
-// Shared-memory ring: kStages tiles of kTile floats, filled by cp.async.bulk (one elected thread
-// issues, an mbarrier per stage counts the bytes), consumed by all 256 threads.  The CTA-wide
-// barrier that ends every tile also tells the issuing thread that the stage may be refilled, so
-// up to (kStages-1) x 16 KB are in flight per CTA while a tile is being compared.
+// Every warp streams its own tiles (warp w takes warp-tiles w, w+8, ... of the slice) with plain
+// 128-bit streaming loads, eight per lane and iteration (1024 elements per warp-tile), exactly
+// like the reduction kernels that reach the HBM roofline.  There is no CTA-wide barrier in the
+// streaming loop; the warps of a CTA meet only at a "rendezvous" when the candidate buffer must be
+// cut (a warp asks for it through a flag that every warp reads once per tile) and at the end.
+// (A shared-memory ring filled by cp.async.bulk was measured first: with one 16 KB stage per CTA
+// tile or one 2 KB stage per warp tile it kept too few bytes in flight per SM and spent its issue
+// slots polling mbarriers: 71-125 us on the [256,151936] batch against 40 us for this form.)
 struct StreamShared {
-    unsigned long long full[kStages];
-    unsigned long long tau;
-    int cnt;
-    int err;
+    unsigned long long tau;         // exclusive threshold: candidate iff word > tau (0 = none yet)
+    unsigned long long samp[256];   // sorted sample of the buffer (cut)
+    unsigned long long wmin[kStreamWarps];  // per-warp bound of the bootstrap
+    float tvf;                      // value of tau's key: the float prefilter compares against it
+    int mode;                       // 0 accept everything, 1 float prefilter, 2 integer compare only
+    int soft;                       // buffer fill at which a cut is requested
+    int cnt;                        // words in the buffer (reservations may overshoot B)
+    int request;                    // a warp asks every warp to the rendezvous
+    int done;                       // warps that have streamed all their tiles
+    int err;                        // a bounded wait gave up (give-up code)
+    int arrive;                     // warps that have arrived at a rendezvous, over all rounds
+    int tmp;
 };
 
 template <bool LARGEST>
 __device__ __forceinline__ float worst_value() { return LARGEST ? -INFINITY : INFINITY; }
 
-// Register path for rows that cannot use bulk copies (element stride != 1, or not 16-byte
-// aligned): this thread's 16 elements of the tile; absent ones get the worst value.
-template <bool LARGEST>
-__device__ __forceinline__ void load_tile_direct(float (&x)[16], const float* slice, long long es,
-                                                 long long len, long long tile_off, int tid) {
+// Descending bitonic sort of 32*E words held by one warp, E per lane, lane-major ("blocked":
+// lane l holds positions l*E .. l*E+E-1).  Strides below E are compare-exchanges inside a lane,
+// the others are shuffles; no shared memory and no barrier.
+template <int E>
+__device__ __forceinline__ void warp_sort_desc(unsigned long long (&v)[E], int lane) {
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        long long e0 = tile_off + ((long long)u * kStreamThreads + tid) * 4;
+    for (int size = 2; size <= 32 * E; size <<= 1) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-            x[4 * u + c] = (e0 + c < len) ? ld_stream1(slice + (e0 + c) * es) : worst_value<LARGEST>();
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            if (stride < E) {
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    if ((e & stride) == 0) {
+                        const bool desc = (((lane * E + e) & size) == 0);
+                        unsigned long long x = v[e], y = v[e | stride];
+                        const bool sw = (x < y) == desc;
+                        v[e] = sw ? y : x;
+                        v[e | stride] = sw ? x : y;
+                    }
+                }
+            } else {
+                const int ls = stride / E;
+                const bool lower = (lane & ls) == 0;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const bool desc = (((lane * E + e) & size) == 0);
+                    unsigned long long o = __shfl_xor_sync(kFull, v[e], ls);
+                    const bool keep_max = lower == desc;
+                    const bool o_bigger = o > v[e];
+                    v[e] = (keep_max == o_bigger) ? o : v[e];
+                }
+            }
+        }
     }
 }
 
-// Cut the buffer back to its k best: zero-fill to a power of two, sort descending, publish the
-// new count and threshold.  Entered by every thread after a barrier that made all appends visible.
-__device__ void compact(unsigned long long* buf, StreamShared* sh, int B, int k, int tid, int nthr) {
+// Cut the candidate buffer back towards its k best and raise the threshold.  Entered by every
+// thread after a barrier that made all appends visible.
+//   n <= 256          warp 0 sorts the buffer in registers: exact, cnt = min(n, k)
+//   n  > 256          sample-select: warp 0 sorts 256 evenly spaced samples, a sample is taken as
+//                     pivot so that about 1.125 k words are expected at or above it, the words
+//                     >= pivot are counted and -- if at least k and at most B/2 -- moved to the
+//                     front (unordered).  O(n) work instead of a sort; the threshold becomes
+//                     pivot - 1, a valid bound because at least k words lie above it.
+//                     If three pivots fail, an exact CTA-wide bitonic sort is used instead.
+//   final             the best min(n, k) are left SORTED in buf[0..), as the output needs them.
+__device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamShared* sh, int B, int k,
+                    int tid, bool final) {
+    const int lane = tid & 31;
     int n = sh->cnt;
     if (n > B) n = B;
+    __syncthreads();   // everyone has read cnt before it is rewritten
+
+    bool exact_needed = final;
+    if (n > 256 && (!final || n > k + (k >> 1) + 64)) {
+        if (tid < 32) {
+            unsigned long long v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = buf[(long long)(tid * 8 + e) * n / 256];
+            warp_sort_desc<8>(v, tid);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sh->samp[tid * 8 + e] = v[e];
+        }
+        __syncthreads();
+        int q = (int)(((long long)256 * (k + (k >> 3) + 16) + n - 1) / n) + 1;
+        bool ok = false;
+        for (int attempt = 0; attempt < 3 && q <= 255; ++attempt, q += 12) {
+            const unsigned long long pivot = sh->samp[q];
+            if (tid == 0) sh->tmp = 0;
+            __syncthreads();
+            int c = 0;
+            for (int i = tid; i < n; i += kStreamThreads) c += buf[i] >= pivot ? 1 : 0;
+            c = __reduce_add_sync(kFull, c);
+            if (lane == 0 && c) atomicAdd(&sh->tmp, c);
+            __syncthreads();
+            const int total = sh->tmp;
+            __syncthreads();
+            if (total >= k && total <= (B >> 1)) {
+                if (tid == 0) sh->tmp = 0;
+                __syncthreads();
+                for (int base = 0; base < n; base += kStreamThreads) {
+                    const int i = base + tid;
+                    unsigned long long w = i < n ? buf[i] : 0ull;
+                    const bool keep = w >= pivot;   // pivot > 0, so padding never passes
+                    const unsigned bal = __ballot_sync(kFull, keep);
+                    int wb = 0;
+                    if (lane == 0 && bal) wb = atomicAdd(&sh->tmp, __popc(bal));
+                    wb = __shfl_sync(kFull, wb, 0);
+                    if (keep) buf2[wb + __popc(bal & ((1u << lane) - 1u))] = w;
+                }
+                __syncthreads();
+                for (int i = tid; i < total; i += kStreamThreads) buf[i] = buf2[i];
+                if (tid == 0) { sh->cnt = total; sh->tau = pivot - 1ull; }
+                __syncthreads();
+                n = total;
+                ok = true;
+                break;
+            }
+        }
+        if (!ok) exact_needed = true;
+    } else {
+        exact_needed = true;
+    }
+    if (!exact_needed) return;
+
+    if (n <= 256) {
+        if (tid < 32) {
+            unsigned long long v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = (tid * 8 + e) < n ? buf[tid * 8 + e] : 0ull;
+            warp_sort_desc<8>(v, tid);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) buf[tid * 8 + e] = v[e];
+            __syncwarp();
+            if (tid == 0) {
+                sh->cnt = n < k ? n : k;
+                sh->tau = n >= k ? buf[k - 1] : 0ull;
+            }
+        }
+        __syncthreads();
+        return;
+    }
     int N = 2;
     while (N < n) N <<= 1;
-    for (int i = n + tid; i < N; i += nthr) buf[i] = 0ull;
+    for (int i = n + tid; i < N; i += kStreamThreads) buf[i] = 0ull;
     __syncthreads();
-    bitonic_desc(buf, N, tid, nthr);
+    bitonic_desc(buf, N, tid, kStreamThreads);
     if (tid == 0) {
         sh->cnt = n < k ? n : k;
         sh->tau = n >= k ? buf[k - 1] : 0ull;
@@ -137,16 +253,20 @@ __device__ void compact(unsigned long long* buf, StreamShared* sh, int B, int k,
     __syncthreads();
 }
 
-template <bool LARGEST, bool BULK>
+// What the rendezvous decided (identical in every thread).
+enum { kActCut = 0, kActFinal = 1 };
+// Give-up codes left in the status word (low byte; the rendezvous round follows in the next bits).
+enum { kErrRendezvous = 2, kErrRetry = 3, kErrPolling = 4 };
+
+template <bool LARGEST, bool VEC>
 __global__ void __launch_bounds__(kStreamThreads, 3)
 topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
                    float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    float* ring = reinterpret_cast<float*>(smem_raw);
-    unsigned long long* buf =
-        reinterpret_cast<unsigned long long*>(smem_raw + (BULK ? (size_t)kStages * kTile * sizeof(float) : 0));
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned long long* buf = reinterpret_cast<unsigned long long*>(smem_raw);
+    unsigned long long* buf2 = buf + g.B;   // B/2 words: target of the sample-select partition
     __shared__ StreamShared sh;
-    const int tid = threadIdx.x, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int s = blockIdx.x;
     const long long r = blockIdx.y;
     const float* row = topk_row(in, g, r);
@@ -154,176 +274,194 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     long long len = g.len - begin;
     if (len > g.chunk) len = g.chunk;
     const float* slice = row + begin * g.es;
-    const int ntiles = (int)((len + kTile - 1) / kTile);
-    const int B = g.B, k = (int)g.k, soft_limit = g.soft;
-
-    // thread 0: start the copy of tile u into its stage (a ragged tail of < 4 floats by hand)
-    auto issue = [&](int u) {
-        const int st = u % kStages;
-        const long long off = (long long)u * kTile;
-        long long n = len - off;
-        if (n > kTile) n = kTile;
-        const int n4 = (int)(n & ~3LL);
-        float* dst = ring + (size_t)st * kTile;
-        for (int i = n4; i < (int)n; ++i) dst[i] = ld_stream1(slice + off + i);
-        if (n4 > 0) {
-            mbar_arrive_expect_tx(&sh.full[st], (unsigned)n4 * 4u);
-            bulk_g2s(dst, slice + off, (unsigned)n4 * 4u, &sh.full[st]);
-        } else {
-            mbar_arrive(&sh.full[st]);
-        }
-    };
+    const int ntiles = (int)((len + kWarpTile - 1) / kWarpTile);       // warp-tiles in the slice
+    const int my_tiles = ntiles > warp ? (ntiles - warp + kStreamWarps - 1) / kStreamWarps : 0;
+    const int B = g.B, k = (int)g.k;
 
     if (tid == 0) {
-        sh.cnt = 0; sh.tau = 0ull; sh.err = 0;
-        if (BULK) {
-            for (int i = 0; i < kStages; ++i) mbar_init(&sh.full[i], 1);
-            fence_mbar_init();
-        }
+        sh.tau = 0ull; sh.tvf = worst_value<LARGEST>(); sh.mode = 0; sh.soft = g.soft;
+        sh.cnt = 0; sh.request = 0; sh.done = 0; sh.err = 0; sh.arrive = 0; sh.tmp = 0;
     }
     __syncthreads();
-    if (BULK && tid == 0)
-        for (int u = 0; u < kStages && u < ntiles; ++u) issue(u);
 
-    unsigned long long tau = 0ull;  // exclusive: candidate iff word > tau
-    float tvf = worst_value<LARGEST>();
-    int mode = 0;                   // 0 accept everything, 1 float compare, 2 integer compare
-
-    for (int t = 0; t < ntiles; ++t) {
-        const long long tile_off = (long long)t * kTile;
-        float x[16];
-        bool timeout = false;
-        if (BULK) {
-            const int st = t % kStages;
-            timeout = !mbar_wait_bounded(&sh.full[st], (unsigned)((t / kStages) & 1));
-            const float4* src = reinterpret_cast<const float4*>(ring + (size_t)st * kTile);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                float4 v = src[u * kStreamThreads + tid];
-                x[4 * u] = v.x; x[4 * u + 1] = v.y; x[4 * u + 2] = v.z; x[4 * u + 3] = v.w;
-            }
-        } else {
-            load_tile_direct<LARGEST>(x, slice, g.es, len, tile_off, tid);
+    // Rendezvous of the eight warps (no warp is appending while it lasts).  The hardware barrier is
+    // entered only after a software arrival count shows that all eight warps are present: a warp
+    // that never comes therefore cannot hang the others -- the wait is bounded, gives up with an
+    // error code in the status word, and everybody leaves.  Cuts the buffer, or, once all warps have
+    // finished streaming (or after a failure), says so -- the same answer in every thread.
+    int round = 0;
+    auto give_up = [&](int code) {
+        if (lane == 0) {
+            *(volatile int*)&sh.err = code;
+            *(volatile int*)&sh.request = 1;
+            if (status) atomicMax(status, code | (round << 8));
         }
-
-        // position of x[4u+c] in the row: begin + tile_off + (u*256 + tid)*4 + c
-        unsigned valid = 0xffffu;
-        if (tile_off + kTile > len) {
-            valid = 0u;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                long long e = tile_off + ((long long)(j >> 2) * kStreamThreads + tid) * 4 + (j & 3);
-                if (e < len) valid |= 1u << j;
-                else x[j] = worst_value<LARGEST>();
-            }
+    };
+    auto rendezvous = [&]() -> int {
+        __syncwarp();
+        ++round;
+        if (lane == 0) atomicAdd(&sh.arrive, 1);
+        const int target = round * kStreamWarps;
+        bool here = false;
+        for (int spin = 0; spin < (1 << 21); ++spin) {
+            if (*(volatile int*)&sh.arrive >= target || *(volatile int*)&sh.err) { here = true; break; }
+            __nanosleep(40);
         }
-        auto idx_of = [&](int j) -> unsigned {
-            return (unsigned)(begin + tile_off + ((long long)(j >> 2) * kStreamThreads + tid) * 4 + (j & 3));
-        };
+        here = __all_sync(kFull, here);
+        if (!here) give_up(kErrRendezvous);
+        if (!here || *(volatile int*)&sh.err) return kActFinal;   // nobody touches the barrier after a failure
+        __syncthreads();
+        const bool fin = *(volatile int*)&sh.done == kStreamWarps;
+        if (fin) return kActFinal;
+        cut(buf, buf2, &sh, B, k, tid, false);
+        if (tid == 0) {
+            const unsigned long long t = sh.tau;
+            sh.mode = t == 0ull ? 0 : ((t >> 32) == 0ull ? 2 : 1);
+            sh.tvf = key_value<LARGEST>((unsigned)(t >> 32));
+            sh.soft = B;            // after the first cut only a full buffer asks for another
+            sh.request = 0;
+        }
+        __syncthreads();
+        return kActCut;
+    };
 
+    // Element j (0..31) of this lane in the warp's tile at offset `off` of the slice is element
+    // ((j>>2)*32 + lane)*4 + (j&3) of the tile: float4 number u*32+lane, component c, j = 4u+c.
+    auto elem_off = [&](long long off, int j) -> long long { return off + ((j >> 2) * 32 + lane) * 4 + (j & 3); };
+
+    // ---- bootstrap (k <= 256, slice of at least one tile per warp): each warp sorts the 32
+    // per-lane maxima of its first tile with shuffles; with j = ceil(k/8) every warp holds j lane
+    // maxima at or above its j-th largest, so the smallest of the eight j-th largest values has at
+    // least 8j >= k elements at or above it: a valid starting threshold.
+    const bool boot = k <= 32 * kStreamWarps && len >= (long long)kStreamWarps * kWarpTile;
+    if (boot) {
+        const long long off = (long long)warp * kWarpTile;
+        unsigned long long gm[1] = {0ull};
+#pragma unroll 4
+        for (int j = 0; j < 32; ++j) {
+            const long long e = elem_off(off, j);
+            unsigned long long w = rank_word<LARGEST>(ld_stream1(slice + e * g.es), (unsigned)(begin + e));
+            gm[0] = w > gm[0] ? w : gm[0];
+        }
+        warp_sort_desc<1>(gm, lane);
+        const unsigned long long jth = __shfl_sync(kFull, gm[0], (k + kStreamWarps - 1) / kStreamWarps - 1);
+        if (lane == 0) sh.wmin[warp] = jth;
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long t = sh.wmin[0];
+            for (int w8 = 1; w8 < kStreamWarps; ++w8) t = sh.wmin[w8] < t ? sh.wmin[w8] : t;
+            t -= 1ull;   // exclusive; the low word of a rank word is never 0, so no borrow from the key
+            sh.tau = t;
+            sh.mode = (t >> 32) == 0ull ? 2 : 1;
+            sh.tvf = key_value<LARGEST>((unsigned)(t >> 32));
+        }
+        __syncthreads();
+    }
+
+    // ---- streaming loop (warp-autonomous)
+    // Hot path: eight 128-bit loads per lane, 32 float compares, one 32-bit mask; nothing else is
+    // kept.  A set bit is a possible candidate: its element is read again by address (an L2 hit),
+    // ranked exactly on the 64-bit word, and appended with one shared-memory atomic.
+    // `abort`: a rendezvous reported a failure somewhere in the CTA; every warp saw the same answer
+    // at the same rendezvous and leaves.
+    bool abort = false;
+    for (int i = 0; i < my_tiles && !abort; ++i) {
+        const long long off = (long long)(warp + i * kStreamWarps) * kWarpTile;
+        const int mode = __shfl_sync(kFull, *(volatile int*)&sh.mode, 0);
         unsigned m = 0u;
         if (mode == 1) {
+            // prefilter: warps run at different places of the row, so an element that ties the
+            // threshold value may still outrank it (lower index): keep ties, decide exactly below
+            const float tvf = *(volatile float*)&sh.tvf;
+            if (VEC && off + kWarpTile <= len) {
+                const float* p = slice + off + lane * 4;
+                float4 v[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                bool p = LARGEST ? (x[j] > tvf) : (x[j] < tvf);
-                m |= p ? (1u << j) : 0u;
-            }
-        } else if (mode == 0 && t == 0 && len >= kTile && k <= kStreamThreads) {
-            // bootstrap: the k-th largest of the 256 per-thread maxima bounds the k-th best from below
-            unsigned long long gm = 0ull;
+                for (int u = 0; u < 8; ++u) v[u] = ld_stream4(p + u * 128);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                unsigned long long w = rank_word<LARGEST>(x[j], idx_of(j));
-                gm = w > gm ? w : gm;
-            }
-            buf[tid] = gm;
-            __syncthreads();
-            bitonic_desc(buf, kStreamThreads, tid, kStreamThreads);
-            tau = buf[k - 1] - 1ull;
-            __syncthreads();
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                m |= (rank_word<LARGEST>(x[j], idx_of(j)) > tau) ? (1u << j) : 0u;
-            // later tiles hold larger indices than the threshold element, so there "word > tau"
-            // is "key > key(tau)", one float compare (tau's low word is never 0, so the -1 above
-            // did not borrow from the key)
-            mode = (tau >> 32) == 0ull ? 2 : 1;
-            tvf = key_value<LARGEST>((unsigned)(tau >> 32));
-        } else if (mode == 0) {
-            m = valid;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                m |= (rank_word<LARGEST>(x[j], idx_of(j)) > tau) ? (1u << j) : 0u;
-            m &= valid;
-        }
-
-        // optimistic append: slots are reserved with one atomic per warp; what does not fit stays
-        // pending and forces a cut of the buffer below
-        unsigned pending = m;
-        auto try_append = [&]() {
-            int n = __popc(pending);
-            int incl = n;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                int o = __shfl_up_sync(kFull, incl, d);
-                if (lane >= d) incl += o;
-            }
-            int total = __shfl_sync(kFull, incl, 31);
-            int base = 0;
-            if (lane == 31) base = atomicAdd(&sh.cnt, total);
-            base = __shfl_sync(kFull, base, 31);
-            int pos = base + incl - n;
-            if (pending) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (pending & (1u << j)) {
-                        if (pos < B) {
-                            buf[pos] = rank_word<LARGEST>(x[j], idx_of(j));
-                            pending &= ~(1u << j);
-                        }
-                        ++pos;
+                for (int u = 0; u < 8; ++u) {
+                    const bool p0 = LARGEST ? (v[u].x >= tvf) : (v[u].x <= tvf);
+                    const bool p1 = LARGEST ? (v[u].y >= tvf) : (v[u].y <= tvf);
+                    const bool p2 = LARGEST ? (v[u].z >= tvf) : (v[u].z <= tvf);
+                    const bool p3 = LARGEST ? (v[u].w >= tvf) : (v[u].w <= tvf);
+                    m |= (p0 ? 1u : 0u) << (4 * u) | (p1 ? 2u : 0u) << (4 * u) | (p2 ? 4u : 0u) << (4 * u) |
+                         (p3 ? 8u : 0u) << (4 * u);
+                }
+            } else {
+#pragma unroll 8
+                for (int j = 0; j < 32; ++j) {
+                    const long long e = elem_off(off, j);
+                    if (e < len) {
+                        const float xv = ld_stream1(slice + e * g.es);
+                        const bool pj = LARGEST ? (xv >= tvf) : (xv <= tvf);
+                        m |= pj ? (1u << j) : 0u;
                     }
                 }
             }
-        };
-        if (__any_sync(kFull, pending != 0u)) try_append();
-
-        const bool soft = tid == 0 && *(volatile int*)&sh.cnt > soft_limit;
-        if (__syncthreads_or((pending != 0u) | soft | timeout)) {
-            if (timeout) sh.err = 1;
-            __syncthreads();
-            if (sh.err) {
-                // a copy never landed: give the copies still in flight a bounded chance to finish,
-                // flag the failure for the host, and leave without touching the outputs
-                if (BULK)
-                    for (int u = t; u < ntiles && u < t + kStages; ++u)
-                        mbar_wait_bounded(&sh.full[u % kStages], (unsigned)((u / kStages) & 1));
-                if (tid == 0 && status) atomicExch(status, 1);
-                return;
-            }
-            while (true) {
-                compact(buf, &sh, B, k, tid, kStreamThreads);
-                tau = sh.tau;
-                if (pending) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if ((pending & (1u << j)) && !(rank_word<LARGEST>(x[j], idx_of(j)) > tau))
-                            pending &= ~(1u << j);
-                }
-                if (__any_sync(kFull, pending != 0u)) try_append();
-                if (!__syncthreads_or(pending != 0u)) break;
-            }
-            mode = tau == 0ull ? 0 : ((tau >> 32) == 0ull ? 2 : 1);
-            tvf = key_value<LARGEST>((unsigned)(tau >> 32));
+        } else {
+            m = 0xffffffffu;   // no usable float threshold yet: every element is ranked exactly
         }
-        // every thread has its tile in registers: the stage can take tile t + kStages
-        if (BULK && tid == 0 && t + kStages < ntiles) issue(t + kStages);
+        int retries = 0;
+        while (__any_sync(kFull, m != 0u)) {
+            if (++retries > 4096) { give_up(kErrRetry); abort = true; break; }   // a cut always frees slots
+            const unsigned long long tau = *(volatile unsigned long long*)&sh.tau;
+            bool over = false;
+            while (m != 0u) {
+                const int j = __ffs(m) - 1;
+                const long long e = elem_off(off, j);
+                if (e < len) {
+                    const float xv = slice[e * g.es];
+                    const unsigned long long w = rank_word<LARGEST>(xv, (unsigned)(begin + e));
+                    if (w > tau) {
+                        const int pos = atomicAdd(&sh.cnt, 1);
+                        if (pos >= B) { over = true; break; }    // keep the bit: retried after the cut
+                        buf[pos] = w;
+                        if (pos + 1 > *(volatile int*)&sh.soft) *(volatile int*)&sh.request = 1;
+                    }
+                }
+                m &= m - 1u;
+            }
+            __syncwarp();
+            if (!__any_sync(kFull, over)) break;
+            // the buffer is full: meet the other warps, cut, and retry what still qualifies
+            if (lane == 0) *(volatile int*)&sh.request = 1;
+            __syncwarp();
+            if (rendezvous() == kActFinal) { abort = true; break; }
+        }
+        // one lane reads the flag for the whole warp: the decision to meet must be warp-uniform
+        __syncwarp();
+        const int req = __shfl_sync(kFull, *(volatile int*)&sh.request | *(volatile int*)&sh.err, 0);
+        if (!abort && req) {
+            if (rendezvous() == kActFinal) abort = true;
+        }
     }
 
-    // final cut: the slice's best min(cnt, k), sorted
-    __syncthreads();
-    compact(buf, &sh, B, k, tid, kStreamThreads);
+    // ---- this warp has no tiles left: keep answering rendezvous requests until all warps are done.
+    // The polling is bounded (about 0.3 s): on give-up the failure is recorded and the kernel ends.
+    if (!abort) {
+        __syncwarp();
+        if (lane == 0) atomicAdd(&sh.done, 1);
+        __syncwarp();
+        for (int spin = 0;; ++spin) {
+            int go = (*(volatile int*)&sh.request != 0) | (*(volatile int*)&sh.done == kStreamWarps) |
+                     (*(volatile int*)&sh.err != 0);
+            go = __shfl_sync(kFull, go, 0);
+            if (go) {
+                if (rendezvous() == kActFinal) break;
+                spin = 0;
+            } else {
+                if (spin > (1 << 21)) { give_up(kErrPolling); break; }
+                __nanosleep(40);
+            }
+        }
+    }
+    if (*(volatile int*)&sh.err) {
+        if (tid == 0 && status) atomicMax(status, 1);
+        return;   // outputs stay unwritten; the host reads the status word
+    }
+
+    // ---- final cut: the slice's best min(cnt, k), sorted
+    cut(buf, buf2, &sh, B, k, tid, true);
     const int cnt = sh.cnt;
     if (ws) {
         unsigned long long* dst = ws + ((size_t)r * g.S + s) * (size_t)k;
@@ -360,8 +498,11 @@ topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long l
     const int k = (int)g.k;
     for (int j = tid; j < k; j += nthr) {
         unsigned idx = word_index(buf[j]);
-        out_idx[r * k + j] = (long long)idx;
-        out_val[r * k + j] = row[(long long)idx * g.es];
+        // a slice kernel that gave up (status word set) leaves its words unwritten: never follow
+        // an index that is not inside the row
+        const bool inside = (long long)idx < g.len;
+        out_idx[r * k + j] = inside ? (long long)idx : -1LL;
+        out_val[r * k + j] = inside ? row[(long long)idx * g.es] : NAN;
     }
 }
 
@@ -515,7 +656,7 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     }
     pl->path = TK_STREAM;
     g.B = pow2_ceil(std::max<long long>(4 * k, 1024));
-    g.soft = (int)std::max<long long>(2 * k, 256);
+    g.soft = (int)std::max<long long>(2 * k, 160);
     // slices: enough CTAs to fill the GPU, each slice at least eight tiles and at least 8k long
     const int sms = sm_count();
     long long want = ceil_div((long long)sms * 4, rows);
@@ -535,7 +676,7 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
 
 template <class K>
 static int allow_smem(K kernel, size_t bytes) {
-    if (bytes > 48 * 1024) {
+    if (bytes + 4096 > 48 * 1024) {   // static shared memory counts against the 48 KB default too
         TPB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
     return TPB200_OK;
@@ -559,12 +700,12 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
     unsigned long long* w = g.S > 1 ? (unsigned long long*)ws : nullptr;
     int* status = device_status_word();
     if (pl.vec) {
-        size_t sm = (size_t)g.B * 8 + (size_t)kStages * kTile * sizeof(float);
+        size_t sm = (size_t)g.B * 12;
         int rc = allow_smem(topk_stream_kernel<LARGEST, true>, sm);
         if (rc) return rc;
         topk_stream_kernel<LARGEST, true><<<grid, kStreamThreads, sm, st>>>(in, g, w, ov, oi, status);
     } else {
-        size_t sm = (size_t)g.B * 8;
+        size_t sm = (size_t)g.B * 12;
         int rc = allow_smem(topk_stream_kernel<LARGEST, false>, sm);
         if (rc) return rc;
         topk_stream_kernel<LARGEST, false><<<grid, kStreamThreads, sm, st>>>(in, g, w, ov, oi, status);
