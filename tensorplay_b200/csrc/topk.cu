@@ -103,7 +103,7 @@ __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom
 // slots polling mbarriers: 71-125 us on the [256,151936] batch against 40 us for this form.)
 struct StreamShared {
     unsigned long long tau;         // exclusive threshold: candidate iff word > tau (0 = none yet)
-    unsigned long long samp[256];   // sorted sample of the buffer (cut)
+    unsigned long long samp[128];   // sorted sample of the buffer (cut)
     unsigned long long wmin[kStreamWarps];  // per-warp bound of the bootstrap
     float tvf;                      // value of tau's key: the float prefilter compares against it
     int mode;                       // 0 accept everything, 1 float prefilter, 2 integer compare only
@@ -158,13 +158,30 @@ __device__ __forceinline__ void warp_sort_desc(unsigned long long (&v)[E], int l
 // Cut the candidate buffer back towards its k best and raise the threshold.  Entered by every
 // thread after a barrier that made all appends visible.
 //   n <= 256          warp 0 sorts the buffer in registers: exact, cnt = min(n, k)
-//   n  > 256          sample-select: warp 0 sorts 256 evenly spaced samples, a sample is taken as
-//                     pivot so that about 1.125 k words are expected at or above it, the words
+//   n  > 256          sample-select: warp 0 sorts 128 evenly spaced samples, a sample is taken as
+//                     pivot so that about 1.2 k words are expected at or above it, the words
 //                     >= pivot are counted and -- if at least k and at most B/2 -- moved to the
 //                     front (unordered).  O(n) work instead of a sort; the threshold becomes
 //                     pivot - 1, a valid bound because at least k words lie above it.
 //                     If three pivots fail, an exact CTA-wide bitonic sort is used instead.
 //   final             the best min(n, k) are left SORTED in buf[0..), as the output needs them.
+// Warp 0 sorts buf[0..n), n <= 256, descending in registers and writes it back padded with zeros
+// to the next multiple of 32*E; the network size follows n (64, 128 or 256 words).
+template <int E>
+__device__ __forceinline__ void warp_sort_smem(unsigned long long* buf, int n, int lane) {
+    unsigned long long v[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) v[e] = (lane * E + e) < n ? buf[lane * E + e] : 0ull;
+    warp_sort_desc<E>(v, lane);
+#pragma unroll
+    for (int e = 0; e < E; ++e) buf[lane * E + e] = v[e];
+}
+__device__ __forceinline__ void warp_sort_upto256(unsigned long long* buf, int n, int lane) {
+    if (n <= 64) warp_sort_smem<2>(buf, n, lane);
+    else if (n <= 128) warp_sort_smem<4>(buf, n, lane);
+    else warp_sort_smem<8>(buf, n, lane);
+}
+
 __device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamShared* sh, int B, int k,
                     int tid, bool final) {
     const int lane = tid & 31;
@@ -175,17 +192,18 @@ __device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamSha
     bool exact_needed = final;
     if (n > 256 && (!final || n > k + (k >> 1) + 64)) {
         if (tid < 32) {
-            unsigned long long v[8];
+            unsigned long long v[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = buf[(long long)(tid * 8 + e) * n / 256];
-            warp_sort_desc<8>(v, tid);
+            for (int e = 0; e < 4; ++e) v[e] = buf[(long long)(tid * 4 + e) * n / 128];
+            warp_sort_desc<4>(v, tid);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) sh->samp[tid * 8 + e] = v[e];
+            for (int e = 0; e < 4; ++e) sh->samp[tid * 4 + e] = v[e];
         }
         __syncthreads();
-        int q = (int)(((long long)256 * (k + (k >> 3) + 16) + n - 1) / n) + 1;
+        // sample rank whose pivot is expected to keep about 1.19 k + 24 words
+        int q = (int)(((long long)128 * (k + (k >> 3) + (k >> 4) + 24) + n - 1) / n) + 1;
         bool ok = false;
-        for (int attempt = 0; attempt < 3 && q <= 255; ++attempt, q += 12) {
+        for (int attempt = 0; attempt < 3 && q <= 127; ++attempt, q += 8) {
             const unsigned long long pivot = sh->samp[q];
             if (tid == 0) sh->tmp = 0;
             __syncthreads();
@@ -226,12 +244,7 @@ __device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamSha
 
     if (n <= 256) {
         if (tid < 32) {
-            unsigned long long v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = (tid * 8 + e) < n ? buf[tid * 8 + e] : 0ull;
-            warp_sort_desc<8>(v, tid);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) buf[tid * 8 + e] = v[e];
+            warp_sort_upto256(buf, n, tid);
             __syncwarp();
             if (tid == 0) {
                 sh->cnt = n < k ? n : k;
@@ -259,7 +272,7 @@ enum { kActCut = 0, kActFinal = 1 };
 enum { kErrRendezvous = 2, kErrRetry = 3, kErrPolling = 4 };
 
 template <bool LARGEST, bool VEC>
-__global__ void __launch_bounds__(kStreamThreads, 3)
+__global__ void __launch_bounds__(kStreamThreads, 4)
 topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
                    float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -337,11 +350,27 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     if (boot) {
         const long long off = (long long)warp * kWarpTile;
         unsigned long long gm[1] = {0ull};
-#pragma unroll 4
-        for (int j = 0; j < 32; ++j) {
-            const long long e = elem_off(off, j);
-            unsigned long long w = rank_word<LARGEST>(ld_stream1(slice + e * g.es), (unsigned)(begin + e));
-            gm[0] = w > gm[0] ? w : gm[0];
+        if (VEC) {
+            const float* p = slice + off + lane * 4;
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = ld_stream4(p + u * 128);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const unsigned b0 = (unsigned)(begin + off) + (u * 32 + lane) * 4;
+                unsigned long long w;
+                w = rank_word<LARGEST>(v[u].x, b0);     gm[0] = w > gm[0] ? w : gm[0];
+                w = rank_word<LARGEST>(v[u].y, b0 + 1); gm[0] = w > gm[0] ? w : gm[0];
+                w = rank_word<LARGEST>(v[u].z, b0 + 2); gm[0] = w > gm[0] ? w : gm[0];
+                w = rank_word<LARGEST>(v[u].w, b0 + 3); gm[0] = w > gm[0] ? w : gm[0];
+            }
+        } else {
+#pragma unroll 8
+            for (int j = 0; j < 32; ++j) {
+                const long long e = elem_off(off, j);
+                unsigned long long w = rank_word<LARGEST>(ld_stream1(slice + e * g.es), (unsigned)(begin + e));
+                gm[0] = w > gm[0] ? w : gm[0];
+            }
         }
         warp_sort_desc<1>(gm, lane);
         const unsigned long long jth = __shfl_sync(kFull, gm[0], (k + kStreamWarps - 1) / kStreamWarps - 1);
