@@ -688,7 +688,7 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     g.soft = (int)std::max<long long>(2 * k, 160);
     // slices: enough CTAs to fill the GPU, each slice at least eight tiles and at least 8k long
     const int sms = sm_count();
-    long long want = ceil_div((long long)sms * 4, rows);
+    long long want = std::max(1LL, ((long long)sms * 4) / rows);   // fill the 4 CTA slots per SM once, never overshoot them
     long long most = std::max(1LL, len / std::max<long long>(8 * kTile, 8 * k));
     long long cap = std::max(1LL, (long long)kMaxSortRow / k);
     long long S = std::max(1LL, std::min(std::min(want, most), cap));
