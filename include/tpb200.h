@@ -152,6 +152,27 @@ int tpb200_topk_merge(const float* cand_val, const int64_t* cand_idx, int64_t n_
                       int largest, const int64_t* list_offsets, int64_t list_len, float* out_val,
                       int64_t* out_idx, void* stream);
 
+/* ---- whole-tensor reduction that allocates nothing and needs no workspace ----------------------
+ * No counterpart in the reference.  For callers that cannot allocate device memory and have no
+ * scratch buffer to pass: a host whose own pool already owns the whole device, or a loop that must
+ * not pay the device-wide synchronisation hidden in cudaMalloc / cudaFree.  Same operators, same
+ * kernels and bit-identical results as tpb200_reduce with reduce_mask = 0 on a contiguous 1-D
+ * tensor of n float32 elements; the partial records live in a TPB200_NOALLOC_SCRATCH_BYTES array
+ * built into the library (each GPU that loads the library holds it until the process exits).
+ *   - n must not exceed TPB200_NOALLOC_MAX_ELEMENTS; larger sizes are refused with
+ *     TPB200_ERR_UNSUPPORTED before anything is launched.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call before any stream capture is begun.
+ *   - The call uses no cudaMalloc, cudaFree or other allocating routine, and never synchronises.
+ *   - All calls on one device share the array.  Nothing in it has to be cleared between calls (the
+ *     first pass overwrites every record the second pass reads), but two calls whose kernels
+ *     overlap on the GPU -- different streams, no ordering between them -- race on it: order them.
+ */
+#define TPB200_NOALLOC_SCRATCH_BYTES (128 * 1024)
+#define TPB200_NOALLOC_MAX_ELEMENTS (1ull << 33)
+int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int64_t n, int64_t correction,
+                              void* out_val, int64_t* out_idx, void* stream);
+
 /* ---- diagnostics ------------------------------------------------------------------------------
  * Every device-side wait in these kernels (on a bulk copy into shared memory) is bounded; a kernel
  * whose wait gave up leaves its outputs unwritten and sets a per-device status word.  This call

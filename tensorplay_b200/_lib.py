@@ -24,7 +24,7 @@ SYMBOLS = [
     "tpb200_last_error", "tpb200_version", "tpb200_reduce", "tpb200_reduce_workspace_bytes",
     "tpb200_topk", "tpb200_topk_workspace_bytes", "tpb200_reduce_partial",
     "tpb200_reduce_partial_workspace_bytes", "tpb200_reduce_combine", "tpb200_topk_merge",
-    "tpb200_device_status",
+    "tpb200_device_status", "tpb200_reduce_all_noalloc",
 ]
 
 _I64P = ctypes.POINTER(ctypes.c_int64)
@@ -69,6 +69,8 @@ def lib() -> ctypes.CDLL:
     L.tpb200_reduce_combine.argtypes = [i, vp, i, i64, i64, vp, vp, vp]
     L.tpb200_topk_merge.restype = i
     L.tpb200_topk_merge.argtypes = [vp, vp, i64, i64, i, vp, i64, vp, vp, vp]
+    L.tpb200_reduce_all_noalloc.restype = i
+    L.tpb200_reduce_all_noalloc.argtypes = [i, vp, i, i64, i64, vp, vp, vp]
     L.tpb200_device_status.restype = i
     L.tpb200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     _lib = L

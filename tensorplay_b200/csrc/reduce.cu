@@ -23,6 +23,8 @@
 #include "host_util.h"
 
 #include <algorithm>
+#include <mutex>
+#include <string>
 #include <vector>
 
 namespace tpb {
@@ -687,6 +689,83 @@ extern "C" int tpb200_reduce_combine(int op, const void* partials, int n_parts, 
         case FAM_MOM: return launch_combine<MomAcc>(p, n_parts, cnt, e, ov, oi, st);
         case FAM_MAX: return launch_combine<ExtAcc<true>>(p, n_parts, cnt, e, ov, oi, st);
         case FAM_MIN: return launch_combine<ExtAcc<false>>(p, n_parts, cnt, e, ov, oi, st);
+    }
+    return fail(TPB200_ERR_INVALID, "internal: bad family");
+}
+
+// ---------------------------------------------------------------- no-allocation variant ------
+// Whole-tensor reduction for callers that may not allocate device memory and have no scratch
+// buffer of their own to lend: a host that has handed every byte of the device to its own memory
+// pool, or a latency-critical loop that cannot afford the implicit device-wide synchronisation of
+// cudaMalloc / cudaFree.  It is the split-row reduction above (row_split_kernel + finalize_kernel)
+// with the packed partials kept in a fixed array inside this module instead of a caller workspace.
+//
+// The array lives in every GPU that loads the library until the process exits (128 KiB each).
+// In host code its name is only a stand-in; the device address is fetched once per device with
+// cudaGetSymbolAddress (with that device current) and handed to the kernels as a plain pointer.
+namespace tpb {
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[TPB200_NOALLOC_SCRATCH_BYTES];
+
+// Device address of the array on the current device (looked up on the first call per device).
+static int noalloc_scratch_address(void** out) {
+    static std::mutex mu;
+    static void* cached[64];
+    int dev = 0;
+    TPB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(TPB200_ERR_UNSUPPORTED, "device ordinal %d is not supported", dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cached[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+        if (!p) return fail(TPB200_ERR_CUDA, "CUDA Error: no device address for the scratch array");
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return TPB200_OK;
+}
+
+}  // namespace tpb
+
+extern "C" int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int64_t n, int64_t correction,
+                                         void* out_val, int64_t* out_idx, void* stream) {
+    Family fam;
+    if (family_of(op, &fam)) return fail(TPB200_ERR_INVALID, "unknown reduction operator %d", op);
+    if (dtype != TPB200_F32) return fail(TPB200_ERR_UNSUPPORTED, "only float32 input is supported (dtype code %d)", dtype);
+    if (n < 0) return fail(TPB200_ERR_INVALID, "negative element count");
+    if ((uint64_t)n > (uint64_t)TPB200_NOALLOC_MAX_ELEMENTS)
+        return fail(TPB200_ERR_UNSUPPORTED, "tpb200_reduce_all_noalloc handles at most %llu elements, %lld given",
+                    (unsigned long long)TPB200_NOALLOC_MAX_ELEMENTS, (long long)n);
+    const bool wants_val = !(op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN);
+    const bool wants_idx = op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN || op == TPB200_OP_MAX_ARGMAX || op == TPB200_OP_MIN_ARGMIN;
+    if (wants_val && (fam == FAM_MAX || fam == FAM_MIN) && n == 0)
+        return fail(TPB200_ERR_EMPTY, "%s(): Expected reduction dim to be non-empty", fam == FAM_MAX ? "max" : "min");
+    if (n > 0 && !in) return fail(TPB200_ERR_INVALID, "input pointer is NULL");
+    if (wants_val && !out_val) return fail(TPB200_ERR_INVALID, "out_val is NULL");
+    if (wants_idx && !out_idx) return fail(TPB200_ERR_INVALID, "out_idx is NULL");
+
+    Plan pl;
+    flat_plan(in, n, &pl);
+    if (pl.ws_bytes > (size_t)TPB200_NOALLOC_SCRATCH_BYTES)
+        return fail(TPB200_ERR_UNSUPPORTED, "this device needs %zu bytes of scratch, the built-in array holds %d",
+                    pl.ws_bytes, (int)TPB200_NOALLOC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    int rc = noalloc_scratch_address(&scratch);
+    if (rc) return rc;
+
+    // Pass 1 overwrites every record that pass 2 reads, so nothing left by an earlier call is used
+    // and nothing has to be cleared.
+    Epilogue e{op, (long long)correction};
+    float* ov = wants_val ? (float*)out_val : nullptr;
+    long long* oi = wants_idx ? (long long*)out_idx : nullptr;
+    cudaStream_t st = (cudaStream_t)stream;
+    const float* x = (const float*)in;
+    switch (fam) {
+        case FAM_SUM: return launch_plan<SumAcc>(pl, x, e, ov, oi, scratch, st);
+        case FAM_MOM: return launch_plan<MomAcc>(pl, x, e, ov, oi, scratch, st);
+        case FAM_MAX: return launch_plan<ExtAcc<true>>(pl, x, e, ov, oi, scratch, st);
+        case FAM_MIN: return launch_plan<ExtAcc<false>>(pl, x, e, ov, oi, scratch, st);
     }
     return fail(TPB200_ERR_INVALID, "internal: bad family");
 }
