@@ -1,0 +1,186 @@
+// Layer 2 of the drop-in: TensorPlay kernels with the exact signatures its DispatchStub casts to
+// (tools/codegen/gen.py:39-54; call site p10/include/Dispatcher.h:46-59), registered for
+// DispatchKey::CUDA under the operator names of p10/src/backend/cuda/ReductionKernels.cu:385-418.
+// Registration is "last one wins" (p10/src/Dispatcher.cpp:13), so loading this library after
+// TensorPlay replaces the cuDNN-based reductions without touching the reference.
+//
+// Compiled against the reference's headers (p10/include + its generated TensorGenerated.h); every
+// number comes from libtpb200.so through the C ABI of include/tpb200.h.  Inputs that the sm_100a
+// kernels do not handle (non-float32) fall through to the kernel that was registered before.
+#include "Tensor.h"
+#include "Dispatcher.h"
+#include "Exception.h"
+
+#include <cstdint>
+#include <optional>
+#include <string>
+#include <vector>
+
+#include "../../../include/tpb200.h"
+
+namespace {
+
+using tensorplay::DType;
+using tensorplay::Tensor;
+using IntList = std::vector<int64_t>;
+
+// Kernels that were registered for CUDA before this library was loaded (may be absent).
+struct Previous {
+    void* sum = nullptr; void* sum_dim = nullptr; void* mean = nullptr; void* mean_dim = nullptr;
+    void* max = nullptr; void* max_dim = nullptr; void* min = nullptr; void* min_dim = nullptr;
+    void* argmax = nullptr; void* argmin = nullptr;
+    void* var = nullptr; void* var_dim = nullptr; void* std_ = nullptr; void* std_dim = nullptr;
+} g_prev;
+
+void* lookup(const char* name) {
+    try {
+        return tensorplay::Dispatcher::singleton().getKernel(name, tensorplay::DispatchKey::CUDA);
+    } catch (...) {
+        return nullptr;
+    }
+}
+
+[[noreturn]] void raise_last() { TP_THROW(RuntimeError, std::string(tpb200_last_error())); }
+
+// (mask, output shape) for a dim list; an empty list reduces every dim.  Errors as
+// compute_reduction_shape (p10/src/backend/cpu/ReductionKernels.cpp:48-58).
+uint64_t mask_and_shape(const Tensor& self, const IntList& dims, bool keepdim, IntList* out_shape) {
+    const int64_t nd = self.dim();
+    uint64_t mask = 0;
+    for (int64_t d : dims) {
+        if (d < 0) d += nd;
+        if (d < 0 || d >= nd) TP_THROW(RuntimeError, "Dimension out of range");
+        mask |= 1ull << d;
+    }
+    const bool all = dims.empty();
+    const IntList shape = static_cast<IntList>(self.shape());
+    for (int64_t i = 0; i < nd; ++i) {
+        const bool red = all || ((mask >> i) & 1);
+        if (red) { if (keepdim && !all) out_shape->push_back(1); }
+        else out_shape->push_back(shape[i]);
+    }
+    return all ? 0 : mask;
+}
+
+// One reduction through the C ABI on the legacy default stream (where the reference launches:
+// ReductionKernels.cu:86-95).  Results and scratch are ordinary TensorPlay tensors.
+Tensor run(int op, const Tensor& self, uint64_t mask, int index_dim, int64_t correction, const IntList& out_shape) {
+    const int nd = (int)self.dim();
+    const IntList sizes = static_cast<IntList>(self.shape());
+    const IntList strides = self.strides();
+    const bool idx = op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN;
+    Tensor out(out_shape, idx ? DType::Int64 : DType::Float32, self.device());
+    const size_t ws_bytes = tpb200_reduce_workspace_bytes(op, TPB200_F32, nd, sizes.data(), strides.data(), mask);
+    Tensor ws;
+    if (ws_bytes) ws = Tensor(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    const int rc = tpb200_reduce(op, self.data_ptr(), TPB200_F32, nd, sizes.data(), strides.data(), mask, index_dim,
+                                 correction, idx ? nullptr : out.data_ptr(), idx ? out.data_ptr<int64_t>() : nullptr,
+                                 ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, nullptr);
+    if (rc != TPB200_OK) raise_last();
+    return out;
+}
+
+bool ours(const Tensor& self) { return self.dtype() == DType::Float32; }
+bool same_dtype(DType d) { return d == DType::Undefined || d == DType::Float32; }
+
+template <class Fn, class... A>
+Tensor fallthrough(void* prev, const char* name, A&&... a) {
+    if (!prev) TP_THROW(NotImplementedError, std::string(name) + " not implemented for this dtype on CUDA");
+    return reinterpret_cast<Fn>(prev)(std::forward<A>(a)...);
+}
+
+// ---- the fourteen kernels ---------------------------------------------------------------------
+Tensor tpb_sum(const Tensor& self, DType dtype) {
+    if (!ours(self) || !same_dtype(dtype)) return fallthrough<Tensor (*)(const Tensor&, DType)>(g_prev.sum, "sum", self, dtype);
+    return run(TPB200_OP_SUM, self, 0, -1, 1, {});
+}
+Tensor tpb_sum_dim(const Tensor& self, const IntList& dim, bool keepdim, DType dtype) {
+    if (!ours(self) || !same_dtype(dtype))
+        return fallthrough<Tensor (*)(const Tensor&, const IntList&, bool, DType)>(g_prev.sum_dim, "sum", self, dim, keepdim, dtype);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_SUM, self, m, -1, 1, shape);
+}
+Tensor tpb_mean(const Tensor& self, DType dtype) {
+    if (!ours(self) || !same_dtype(dtype)) return fallthrough<Tensor (*)(const Tensor&, DType)>(g_prev.mean, "mean", self, dtype);
+    return run(TPB200_OP_MEAN, self, 0, -1, 1, {});
+}
+Tensor tpb_mean_dim(const Tensor& self, const IntList& dim, bool keepdim, DType dtype) {
+    if (!ours(self) || !same_dtype(dtype))
+        return fallthrough<Tensor (*)(const Tensor&, const IntList&, bool, DType)>(g_prev.mean_dim, "mean", self, dim, keepdim, dtype);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_MEAN, self, m, -1, 1, shape);
+}
+Tensor tpb_max(const Tensor& self) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&)>(g_prev.max, "max", self);
+    return run(TPB200_OP_MAX, self, 0, -1, 1, {});
+}
+Tensor tpb_max_dim(const Tensor& self, const IntList& dim, bool keepdim) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, const IntList&, bool)>(g_prev.max_dim, "max", self, dim, keepdim);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_MAX, self, m, -1, 1, shape);
+}
+Tensor tpb_min(const Tensor& self) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&)>(g_prev.min, "min", self);
+    return run(TPB200_OP_MIN, self, 0, -1, 1, {});
+}
+Tensor tpb_min_dim(const Tensor& self, const IntList& dim, bool keepdim) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, const IntList&, bool)>(g_prev.min_dim, "min", self, dim, keepdim);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_MIN, self, m, -1, 1, shape);
+}
+Tensor arg_common(int op, void* prev, const char* name, const Tensor& self, std::optional<int64_t> dim, bool keepdim) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, std::optional<int64_t>, bool)>(prev, name, self, dim, keepdim);
+    if (!dim.has_value()) return run(op, self, 0, -1, 1, {});
+    int64_t d = *dim;
+    if (d < 0) d += self.dim();
+    if (d < 0 || d >= self.dim()) TP_THROW(RuntimeError, "Dimension out of range");
+    IntList shape; const uint64_t m = mask_and_shape(self, IntList{d}, keepdim, &shape);
+    return run(op, self, m, (int)d, 1, shape);
+}
+Tensor tpb_argmax(const Tensor& self, std::optional<int64_t> dim, bool keepdim) {
+    return arg_common(TPB200_OP_ARGMAX, g_prev.argmax, "argmax", self, dim, keepdim);
+}
+Tensor tpb_argmin(const Tensor& self, std::optional<int64_t> dim, bool keepdim) {
+    return arg_common(TPB200_OP_ARGMIN, g_prev.argmin, "argmin", self, dim, keepdim);
+}
+Tensor tpb_var(const Tensor& self, int64_t correction) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, int64_t)>(g_prev.var, "var", self, correction);
+    return run(TPB200_OP_VAR, self, 0, -1, correction, {});
+}
+Tensor tpb_var_dim(const Tensor& self, const IntList& dim, int64_t correction, bool keepdim) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, const IntList&, int64_t, bool)>(g_prev.var_dim, "var", self, dim, correction, keepdim);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_VAR, self, m, -1, correction, shape);
+}
+Tensor tpb_std(const Tensor& self, int64_t correction) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, int64_t)>(g_prev.std_, "std", self, correction);
+    return run(TPB200_OP_STD, self, 0, -1, correction, {});
+}
+Tensor tpb_std_dim(const Tensor& self, const IntList& dim, int64_t correction, bool keepdim) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, const IntList&, int64_t, bool)>(g_prev.std_dim, "std", self, dim, correction, keepdim);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_STD, self, m, -1, correction, shape);
+}
+
+}  // namespace
+
+namespace tensorplay {
+
+TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
+    g_prev.sum = lookup("sum");         g_prev.sum_dim = lookup("sum.dim_IntList");
+    g_prev.mean = lookup("mean");       g_prev.mean_dim = lookup("mean.dim");
+    g_prev.max = lookup("max");         g_prev.max_dim = lookup("max.dim");
+    g_prev.min = lookup("min");         g_prev.min_dim = lookup("min.dim");
+    g_prev.argmax = lookup("argmax");   g_prev.argmin = lookup("argmin");
+    g_prev.var = lookup("var");         g_prev.var_dim = lookup("var.dim");
+    g_prev.std_ = lookup("std");        g_prev.std_dim = lookup("std.dim");
+    m.impl("sum", tpb_sum);             m.impl("sum.dim_IntList", tpb_sum_dim);
+    m.impl("mean", tpb_mean);           m.impl("mean.dim", tpb_mean_dim);
+    m.impl("max", tpb_max);             m.impl("max.dim", tpb_max_dim);
+    m.impl("min", tpb_min);             m.impl("min.dim", tpb_min_dim);
+    m.impl("argmax", tpb_argmax);       m.impl("argmin", tpb_argmin);
+    m.impl("var", tpb_var);             m.impl("var.dim", tpb_var_dim);
+    m.impl("std", tpb_std);             m.impl("std.dim", tpb_std_dim);
+}
+
+}  // namespace tensorplay

@@ -1,0 +1,90 @@
+// TEST INFRASTRUCTURE.  Exercises the drop-in boundary end to end at the C++ level: TensorPlay's own
+// generated Tensor methods, called on CUDA tensors, must resolve through TensorPlay's Dispatcher to
+// the kernels registered by tensorplay_b200/csrc/adapter/tensorplay_adapter.cpp and agree with the
+// same methods run on the CPU copy of the data (the reference's CPU kernels).
+// Built by oracle/build_adapter_check.sh against a TensorPlay checkout; run by tests/test_gpu_adapter.py.
+#include "Tensor.h"
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+using namespace tensorplay;
+
+static Tensor to_cuda(const Tensor& c) {
+    Tensor g(static_cast<std::vector<int64_t>>(c.shape()), c.dtype(), Device(DeviceType::CUDA, 0));
+    cudaMemcpy(g.data_ptr(), c.data_ptr(), c.numel() * c.itemsize(), cudaMemcpyHostToDevice);
+    return g;
+}
+template <class T>
+static std::vector<T> to_host(const Tensor& g) {
+    std::vector<T> h(g.numel());
+    cudaDeviceSynchronize();
+    cudaMemcpy(h.data(), g.data_ptr(), h.size() * sizeof(T), cudaMemcpyDeviceToHost);
+    return h;
+}
+static int fails = 0, checks = 0;
+static void close_f(const char* what, const Tensor& gpu, const Tensor& cpu, double rel, double abs_tol) {
+    ++checks;
+    auto g = to_host<float>(gpu);
+    const float* c = cpu.data_ptr<float>();
+    if ((int64_t)g.size() != cpu.numel() || static_cast<std::vector<int64_t>>(gpu.shape()) != static_cast<std::vector<int64_t>>(cpu.shape())) {
+        printf("FAIL %s: shape\n", what); ++fails; return;
+    }
+    for (size_t i = 0; i < g.size(); ++i)
+        if (!(std::fabs((double)g[i] - c[i]) <= rel * std::fabs((double)c[i]) + abs_tol)) {
+            printf("FAIL %s: [%zu] gpu %.9g cpu %.9g\n", what, i, g[i], c[i]); ++fails; return;
+        }
+}
+static void equal_i(const char* what, const Tensor& gpu, const Tensor& cpu) {
+    ++checks;
+    auto g = to_host<int64_t>(gpu);
+    const int64_t* c = cpu.data_ptr<int64_t>();
+    for (size_t i = 0; i < g.size(); ++i)
+        if (g[i] != c[i]) { printf("FAIL %s: [%zu] gpu %lld cpu %lld\n", what, i, (long long)g[i], (long long)c[i]); ++fails; return; }
+}
+static void equal_bits(const char* what, const Tensor& gpu, const Tensor& cpu) {
+    ++checks;
+    auto g = to_host<float>(gpu);
+    if (std::memcmp(g.data(), cpu.data_ptr<float>(), g.size() * 4) != 0) { printf("FAIL %s: bits differ\n", what); ++fails; }
+}
+
+int main() {
+    setvbuf(stdout, nullptr, _IONBF, 0);
+    const int64_t R = 64, C = 1000;
+    std::vector<float> v(R * C);
+    unsigned s = 12345u;
+    for (auto& x : v) { s = s * 1664525u + 1013904223u; x = (float)((int)(s >> 8) % 2001 - 1000) / 250.0f; }
+    v[7] = v[3];   // ties
+    Tensor c = Tensor::tensor<float>(v).reshape({R, C});
+    Tensor g = to_cuda(c);
+    if (!g.device().is_cuda()) { printf("FAIL: no CUDA tensor\n"); return 2; }
+    const double tol = 2e-3;   // the reference's CPU dim-sum accumulates sequentially in float32
+    close_f("sum(dim=1)", g.sum({1}, false, DType::Undefined), c.sum({1}, false, DType::Undefined), 1e-5, tol);
+    close_f("sum(dim=0,keepdim)", g.sum({0}, true, DType::Undefined), c.sum({0}, true, DType::Undefined), 1e-5, tol);
+    close_f("sum()", g.sum(DType::Undefined), c.sum(DType::Undefined), 1e-5, tol);
+    close_f("mean(dim=-1)", g.mean({-1}, false, DType::Undefined), c.mean({-1}, false, DType::Undefined), 1e-5, 1e-5);
+    close_f("mean()", g.mean(DType::Undefined), c.mean(DType::Undefined), 1e-5, 1e-6);
+    close_f("var(dim=1)", g.var({1}, 1, false), c.var({1}, 1, false), 1e-4, 0);
+    close_f("std()", g.std(1), c.std(1), 1e-4, 0);
+    equal_bits("max(dim=1)", g.max({1}, false), c.max({1}, false));
+    equal_bits("min(dim=0)", g.min({0}, false), c.min({0}, false));
+    equal_bits("max()", g.max(), c.max());
+    equal_i("argmax(1)", g.argmax(std::optional<int64_t>(1), false), c.argmax(std::optional<int64_t>(1), false));
+    equal_i("argmin(0,keepdim)", g.argmin(std::optional<int64_t>(0), true), c.argmin(std::optional<int64_t>(0), true));
+    equal_i("argmax()", g.argmax(std::nullopt, false), c.argmax(std::nullopt, false));
+    // a strided view (the transpose, built on the same storage) is consumed in place
+    Tensor gt(g.impl()->storage(), {C, R}, {1, C}, DType::Float32, 0);
+    Tensor ct(c.impl()->storage(), {C, R}, {1, C}, DType::Float32, 0);
+    close_f("sum(dim=0) of a transposed view", gt.sum({0}, false, DType::Undefined), ct.sum({0}, false, DType::Undefined), 1e-5, tol);
+    equal_i("argmax(1) of a transposed view", gt.argmax(std::optional<int64_t>(1), false), ct.argmax(std::optional<int64_t>(1), false));
+    // errors keep the reference's type and message
+    try { g.sum({2}, false, DType::Undefined); printf("FAIL: no error for a bad dim\n"); ++fails; }
+    catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "Dimension out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }
+    printf("adapter_check: %d checks, %d failures\n", checks, fails);
+    fflush(stdout);
+    return fails ? 1 : 0;
+}

@@ -1,0 +1,21 @@
+"""GPU test of the drop-in boundary at the C++ level: oracle/_ref/adapter_check (built by
+oracle/build_adapter_check.sh where a TensorPlay checkout exists) calls TensorPlay's own generated
+Tensor::sum/mean/var/std/max/min/argmax/argmin on CUDA tensors; they must dispatch through
+TensorPlay's Dispatcher to the kernels registered by tensorplay_b200/csrc/adapter/ and agree with
+the reference's CPU kernels on the same data."""
+import os
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BIN = os.path.join(ROOT, "oracle", "_ref", "adapter_check")
+
+
+def test_tensorplay_dispatches_to_the_new_kernels(cuda):
+    if not os.path.exists(BIN):
+        pytest.skip("adapter_check was not built (needs a TensorPlay checkout at build time)")
+    r = subprocess.run([BIN], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "0 failures" in r.stdout
