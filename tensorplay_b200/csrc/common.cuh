@@ -127,18 +127,27 @@ struct MomAcc {
     __device__ __forceinline__ void finish_thread() {
         n = (double)c;
         if (c > 0u) {
-            double s1 = mean;
-            mean = k + s1 / n;
-            m2 = m2 - s1 * s1 / n;
+            const double inv = 1.0 / n;
+            const double s1 = mean;
+            mean = fma(s1, inv, k);
+            m2 = m2 - s1 * s1 * inv;
             if (m2 < 0.0) m2 = 0.0;
         }
     }
+    // Chan's pairwise update.  Equal counts -- every level of a tree over threads that saw the same
+    // number of elements -- need no division at all.
     __device__ __forceinline__ void merge(const MomAcc& o) {
         if (o.n == 0.0) return;
         if (n == 0.0) { n = o.n; mean = o.mean; m2 = o.m2; return; }
-        double nt = n + o.n;
-        double delta = o.mean - mean;
-        double w = o.n / nt;
+        const double delta = o.mean - mean;
+        if (n == o.n) {
+            mean = fma(delta, 0.5, mean);
+            m2 = m2 + o.m2 + delta * delta * (n * 0.5);
+            n = n + n;
+            return;
+        }
+        const double nt = n + o.n;
+        const double w = o.n / nt;
         mean = fma(delta, w, mean);
         m2 = m2 + o.m2 + delta * delta * n * w;
         n = nt;

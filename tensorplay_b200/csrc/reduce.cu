@@ -65,8 +65,13 @@ row_warp_kernel(const float* __restrict__ in, RowGeom g, Epilogue e, float* ov, 
     const float* p = row_base(in, g, r);
     Acc acc;
     acc.init();
-    for (long long s = 0; s < g.nseg; ++s)
-        scan_contig<4>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
+    if (g.seglen >= 2048) {   // long runs: eight loads in flight per lane
+        for (long long s = 0; s < g.nseg; ++s)
+            scan_contig<8>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
+    } else {
+        for (long long s = 0; s < g.nseg; ++s)
+            scan_contig<4>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
+    }
     acc.finish_thread();
     warp_combine(acc);
     if (lane == 0) write_result(acc, e, (double)g.nseg * (double)g.seglen, ov, oi, r);
@@ -428,7 +433,9 @@ static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64
         else if (force == ST_ROW_WARP) st = ST_ROW_WARP;
         else if (force == ST_ROW_CTA) st = ST_ROW_CTA;
         else if (S >= 2) st = ST_ROW_SPLIT;
-        else if (g.nseg == 1 && L <= 1024) st = ST_ROW_WARP;
+        else if (g.nseg == 1 && (L <= 1024 || (L <= 8192 && outs >= 8LL * sms))) st = ST_ROW_WARP;
+        // (rows of up to 32 KB with at least one warp-row per warp slot of the GPU: a warp per row
+        //  needs no shared-memory combine and a fraction of the instructions of a CTA per row)
         else st = ST_ROW_CTA;
 
         pl->st = st;
