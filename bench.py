@@ -40,7 +40,7 @@ NOMINAL_PEAK_GBS = 8000.0
 # DRAM traffic per launch of the dominant kernel from one ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum; summaries under profiles/).  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    "c2": 156_340_736 + 5_600_000,   # profiles/topk_stream_c2.md
+    "c2": 155_772_160 + 4_080_640,   # profiles/topk_stream_c2.md
 }
 
 
@@ -401,6 +401,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")   # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     tpb._lib.lib()
     peak, peak_kind = measured_peak()

@@ -26,10 +26,8 @@
 
 namespace tpb {
 
-constexpr int kStreamThreads = 256;
-constexpr int kStreamWarps = kStreamThreads / 32;
+constexpr int kMaxStreamWarps = 16;                            // a streaming CTA has 8 or 16 warps
 constexpr int kWarpTile = 32 * 32;                            // 1024 elements per warp and iteration
-constexpr int kTile = kStreamWarps * kWarpTile;               // elements all warps consume per round
 constexpr int kSortThreads = 512;
 constexpr int kMaxStreamK = 2048;                             // largest k of the streaming path
 constexpr int kMaxSortRow = 16384;                            // longest row sorted whole in smem
@@ -84,6 +82,7 @@ struct TopkGeom {
     int S;                // slices per row
     int B;                // candidate buffer capacity (power of two)
     int soft;             // buffer fill that triggers a cut at the next tile boundary
+    int warps;            // warps per streaming CTA (8 or 16)
 };
 
 __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom& g, long long r) {
@@ -104,7 +103,7 @@ __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom
 struct StreamShared {
     unsigned long long tau;         // exclusive threshold: candidate iff word > tau (0 = none yet)
     unsigned long long samp[128];   // sorted sample of the buffer (cut)
-    unsigned long long wmin[kStreamWarps];  // per-warp bound of the bootstrap
+    unsigned long long wmin[kMaxStreamWarps];  // per-warp bound of the bootstrap
     float tvf;                      // value of tau's key: the float prefilter compares against it
     int mode;                       // 0 accept everything, 1 float prefilter, 2 integer compare only
     int soft;                       // buffer fill at which a cut is requested
@@ -183,7 +182,7 @@ __device__ __forceinline__ void warp_sort_upto256(unsigned long long* buf, int n
 }
 
 __device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamShared* sh, int B, int k,
-                    int tid, bool final) {
+                    int tid, int nthr, bool final) {
     const int lane = tid & 31;
     int n = sh->cnt;
     if (n > B) n = B;
@@ -208,7 +207,7 @@ __device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamSha
             if (tid == 0) sh->tmp = 0;
             __syncthreads();
             int c = 0;
-            for (int i = tid; i < n; i += kStreamThreads) c += buf[i] >= pivot ? 1 : 0;
+            for (int i = tid; i < n; i += nthr) c += buf[i] >= pivot ? 1 : 0;
             c = __reduce_add_sync(kFull, c);
             if (lane == 0 && c) atomicAdd(&sh->tmp, c);
             __syncthreads();
@@ -217,7 +216,7 @@ __device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamSha
             if (total >= k && total <= (B >> 1)) {
                 if (tid == 0) sh->tmp = 0;
                 __syncthreads();
-                for (int base = 0; base < n; base += kStreamThreads) {
+                for (int base = 0; base < n; base += nthr) {
                     const int i = base + tid;
                     unsigned long long w = i < n ? buf[i] : 0ull;
                     const bool keep = w >= pivot;   // pivot > 0, so padding never passes
@@ -228,7 +227,7 @@ __device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamSha
                     if (keep) buf2[wb + __popc(bal & ((1u << lane) - 1u))] = w;
                 }
                 __syncthreads();
-                for (int i = tid; i < total; i += kStreamThreads) buf[i] = buf2[i];
+                for (int i = tid; i < total; i += nthr) buf[i] = buf2[i];
                 if (tid == 0) { sh->cnt = total; sh->tau = pivot - 1ull; }
                 __syncthreads();
                 n = total;
@@ -256,9 +255,9 @@ __device__ void cut(unsigned long long* buf, unsigned long long* buf2, StreamSha
     }
     int N = 2;
     while (N < n) N <<= 1;
-    for (int i = n + tid; i < N; i += kStreamThreads) buf[i] = 0ull;
+    for (int i = n + tid; i < N; i += nthr) buf[i] = 0ull;
     __syncthreads();
-    bitonic_desc(buf, N, tid, kStreamThreads);
+    bitonic_desc(buf, N, tid, nthr);
     if (tid == 0) {
         sh->cnt = n < k ? n : k;
         sh->tau = n >= k ? buf[k - 1] : 0ull;
@@ -271,14 +270,16 @@ enum { kActCut = 0, kActFinal = 1 };
 // Give-up codes left in the status word (low byte; the rendezvous round follows in the next bits).
 enum { kErrRendezvous = 2, kErrRetry = 3, kErrPolling = 4 };
 
-template <bool LARGEST, bool VEC>
-__global__ void __launch_bounds__(kStreamThreads, 4)
+template <bool LARGEST, bool VEC, int NW>
+__global__ void __launch_bounds__(NW * 32, 32 / NW)
 topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
                    float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned long long* buf = reinterpret_cast<unsigned long long*>(smem_raw);
     unsigned long long* buf2 = buf + g.B;   // B/2 words: target of the sample-select partition
     __shared__ StreamShared sh;
+    constexpr int kStreamWarps = NW;
+    constexpr int kStreamThreads = NW * 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int s = blockIdx.x;
     const long long r = blockIdx.y;
@@ -326,7 +327,7 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
         __syncthreads();
         const bool fin = *(volatile int*)&sh.done == kStreamWarps;
         if (fin) return kActFinal;
-        cut(buf, buf2, &sh, B, k, tid, false);
+        cut(buf, buf2, &sh, B, k, tid, kStreamThreads, false);
         if (tid == 0) {
             const unsigned long long t = sh.tau;
             sh.mode = t == 0ull ? 0 : ((t >> 32) == 0ull ? 2 : 1);
@@ -490,7 +491,7 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     }
 
     // ---- final cut: the slice's best min(cnt, k), sorted
-    cut(buf, buf2, &sh, B, k, tid, true);
+    cut(buf, buf2, &sh, B, k, tid, kStreamThreads, true);
     const int cnt = sh.cnt;
     if (ws) {
         unsigned long long* dst = ws + ((size_t)r * g.S + s) * (size_t)k;
@@ -685,11 +686,19 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     }
     pl->path = TK_STREAM;
     g.B = pow2_ceil(std::max<long long>(4 * k, 1024));
-    g.soft = (int)std::max<long long>(2 * k, 160);
-    // slices: enough CTAs to fill the GPU, each slice at least eight tiles and at least 8k long
+    // first cut early: handling a candidate costs far more than skipping an element, and only a cut
+    // tightens the threshold (measured on [256,151936], k = 50: 320 words beats 160 and 1024)
+    g.soft = (int)std::min<long long>(g.B / 2, std::max<long long>(320, 3 * k));
     const int sms = sm_count();
-    long long want = std::max(1LL, ((long long)sms * 4) / rows);   // fill the 4 CTA slots per SM once, never overshoot them
-    long long most = std::max(1LL, len / std::max<long long>(8 * kTile, 8 * k));
+    // CTA width: one 16-warp CTA per row when there are enough long rows to fill the GPU that way
+    // (half as many bootstraps / cuts and no merge kernel), otherwise 8-warp CTAs, several per row.
+    g.warps = (rows >= sms && len >= 64 * 1024) ? 16 : 8;
+    if (const char* fw = getenv("TPB200_TOPK_WARPS")) g.warps = atoi(fw) == 16 ? 16 : 8;   // experiments
+    // slices: fill the CTA slots of the GPU once, never overshoot them; each slice at least eight
+    // rounds of all warps and at least 8k long
+    const int slots = sms * (g.warps == 16 ? 2 : 4);
+    long long want = std::max(1LL, (long long)slots / rows);
+    long long most = std::max(1LL, len / std::max<long long>(8LL * g.warps * kWarpTile, 8 * k));
     long long cap = std::max(1LL, (long long)kMaxSortRow / k);
     long long S = std::max(1LL, std::min(std::min(want, most), cap));
     const char* fs = getenv("TPB200_TOPK_SLICES");
@@ -728,17 +737,17 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
     dim3 grid((unsigned)g.S, (unsigned)g.rows);
     unsigned long long* w = g.S > 1 ? (unsigned long long*)ws : nullptr;
     int* status = device_status_word();
-    if (pl.vec) {
-        size_t sm = (size_t)g.B * 12;
-        int rc = allow_smem(topk_stream_kernel<LARGEST, true>, sm);
-        if (rc) return rc;
-        topk_stream_kernel<LARGEST, true><<<grid, kStreamThreads, sm, st>>>(in, g, w, ov, oi, status);
-    } else {
-        size_t sm = (size_t)g.B * 12;
-        int rc = allow_smem(topk_stream_kernel<LARGEST, false>, sm);
-        if (rc) return rc;
-        topk_stream_kernel<LARGEST, false><<<grid, kStreamThreads, sm, st>>>(in, g, w, ov, oi, status);
-    }
+    const size_t sm = (size_t)g.B * 12;
+    const int threads = g.warps * 32;
+#define TPB_LAUNCH_STREAM(V, W)                                                                          \
+    do {                                                                                                 \
+        int rc = allow_smem(topk_stream_kernel<LARGEST, V, W>, sm);                                      \
+        if (rc) return rc;                                                                               \
+        topk_stream_kernel<LARGEST, V, W><<<grid, threads, sm, st>>>(in, g, w, ov, oi, status);          \
+    } while (0)
+    if (pl.vec) { if (g.warps == 16) TPB_LAUNCH_STREAM(true, 16); else TPB_LAUNCH_STREAM(true, 8); }
+    else        { if (g.warps == 16) TPB_LAUNCH_STREAM(false, 16); else TPB_LAUNCH_STREAM(false, 8); }
+#undef TPB_LAUNCH_STREAM
     TPB_LAUNCH_OK("topk_stream_kernel");
     if (g.S > 1) {
         size_t msm = (size_t)pl.mergeN * 8;
