@@ -408,7 +408,7 @@ def main():
 
     def run_workload(wl, steps, warmup, sampler=None):
         out = []
-        graph_ok = not args.no_graph and not (wl == "c4" and world > 1)   # no collective inside a graph
+        graph_ok = not args.no_graph   # the all-gather of the sharded whole-tensor path is captured too
         for n, case in enumerate(build_cases(torch, tpb, dev, wl, rank, world, seed=1234)):
             if sampler is not None and n == 0:
                 with sampler:
