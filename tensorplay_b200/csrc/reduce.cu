@@ -366,7 +366,7 @@ static Strategy forced_strategy() {
 }
 
 static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64_t* strides,
-                     uint64_t mask, Plan* pl) {
+                     uint64_t mask, Family fam, Plan* pl) {
     if (ndim < 0 || ndim > TPB200_MAX_DIMS)
         return fail(TPB200_ERR_UNSUPPORTED, "tensors of rank %d are not supported (max %d)", ndim, TPB200_MAX_DIMS);
     if (ndim > 0 && (!sizes || !strides)) return fail(TPB200_ERR_INVALID, "sizes/strides must not be NULL");
@@ -463,9 +463,15 @@ static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64
         pl->tiles = (int)ceil_div(pl->I, (long long)pl->tx_n * pl->vec);
         const int ny = 256 / pl->tx_n;
         long long ctas = pl->O * pl->tiles;
-        long long want = ceil_div((long long)sms * 8, ctas);
+        // sum / extremum: one wave -- as many slices as keep all CTAs resident at once (4 CTAs of 256
+        // threads per SM); measured on [64,4096,512] over dim 1: 2 slices (512 CTAs) 80 us, 5 slices
+        // (1280 CTAs) 95 us.  The variance kernel is bound by the fp64 pipe and its three resident
+        // CTAs per SM, and is fastest with several waves of smaller CTAs (5 slices 111 us, 2: 146 us).
+        long long want = fam == FAM_MOM ? ceil_div((long long)sms * 8, ctas)
+                                        : std::max(1LL, ((long long)sms * 4) / std::max(1LL, ctas));
         long long most = std::max(1LL, pl->L / ((long long)ny * 8));
         int S = (int)std::max(1LL, std::min(std::min(want, most), 65535LL));
+        if (const char* fs = getenv("TPB200_COL_SPLITS")) S = (int)std::max(1LL, std::min<long long>(atoi(fs), most));   // experiments
         pl->lchunk = ceil_div(pl->L, S);
         pl->S = (int)ceil_div(pl->L, pl->lchunk);
         if (pl->S > 1) pl->ws_bytes = (size_t)pl->O * pl->S * pl->I * sizeof(Packed);
@@ -545,11 +551,11 @@ using namespace tpb;
 
 extern "C" size_t tpb200_reduce_workspace_bytes(int op, int dtype, int ndim, const int64_t* sizes,
                                                 const int64_t* strides, uint64_t reduce_mask) {
-    (void)op;
-    if (dtype != TPB200_F32) return 0;
+    Family fam;
+    if (dtype != TPB200_F32 || family_of(op, &fam)) return 0;
     Plan pl;
     // alignment of the data pointer does not change the workspace size
-    if (make_plan((const void*)16, ndim, sizes, strides, reduce_mask, &pl) != TPB200_OK) return 0;
+    if (make_plan((const void*)16, ndim, sizes, strides, reduce_mask, fam, &pl) != TPB200_OK) return 0;
     return pl.ws_bytes;
 }
 
@@ -563,7 +569,7 @@ extern "C" int tpb200_reduce(int op, const void* in, int dtype, int ndim, const 
     const bool wants_val = !(op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN);
     const bool wants_idx = op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN || op == TPB200_OP_MAX_ARGMAX || op == TPB200_OP_MIN_ARGMIN;
     Plan pl;
-    int rc = make_plan(in, ndim, sizes, strides, reduce_mask, &pl);
+    int rc = make_plan(in, ndim, sizes, strides, reduce_mask, fam, &pl);
     if (rc) return rc;
     if (wants_idx) {
         const uint64_t all = ndim == 0 ? 0 : ((1ull << ndim) - 1);
