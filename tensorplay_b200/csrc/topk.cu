@@ -690,9 +690,9 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     // tightens the threshold (measured on [256,151936], k = 50: 320 words beats 160 and 1024)
     g.soft = (int)std::min<long long>(g.B / 2, std::max<long long>(320, 3 * k));
     const int sms = sm_count();
-    // CTA width: one 16-warp CTA per row when there are enough long rows to fill the GPU that way
-    // (half as many bootstraps / cuts and no merge kernel), otherwise 8-warp CTAs, several per row.
-    g.warps = (rows >= sms && len >= 64 * 1024) ? 16 : 8;
+    // CTA width: 16 warps for long rows (half as many bootstraps / cuts as two 8-warp slices and,
+    // with one CTA per row, no merge kernel), 8 warps for rows below 64 K elements.
+    g.warps = len >= 64 * 1024 ? 16 : 8;
     if (const char* fw = getenv("TPB200_TOPK_WARPS")) g.warps = atoi(fw) == 16 ? 16 : 8;   // experiments
     // slices: fill the CTA slots of the GPU once, never overshoot them; each slice at least eight
     // rounds of all warps and at least 8k long
@@ -700,6 +700,9 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     long long want = std::max(1LL, (long long)slots / rows);
     long long most = std::max(1LL, len / std::max<long long>(8LL * g.warps * kWarpTile, 8 * k));
     long long cap = std::max(1LL, (long long)kMaxSortRow / k);
+    // every slice of a large-k row pays its own cuts towards k: measured on [64..256, 2^20], k = 1024,
+    // two slices per row are the most that still pay off
+    if (k > 256) want = std::min(want, 2LL);
     long long S = std::max(1LL, std::min(std::min(want, most), cap));
     const char* fs = getenv("TPB200_TOPK_SLICES");
     if (fs) S = std::max(1LL, std::min((long long)atoi(fs), cap));
