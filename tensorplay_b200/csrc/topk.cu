@@ -689,6 +689,8 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     // first cut early: handling a candidate costs far more than skipping an element, and only a cut
     // tightens the threshold (measured on [256,151936], k = 50: 320 words beats 160 and 1024)
     g.soft = (int)std::min<long long>(g.B / 2, std::max<long long>(320, 3 * k));
+    if (const char* fb = getenv("TPB200_TOPK_B")) g.B = std::max(g.B, pow2_ceil(atoi(fb)));                        // experiments
+    if (const char* fso = getenv("TPB200_TOPK_SOFT")) g.soft = std::min(g.B - 1, std::max(atoi(fso), (int)k + 1));   // experiments
     const int sms = sm_count();
     // CTA width: 16 warps for long rows (half as many bootstraps / cuts as two 8-warp slices and,
     // with one CTA per row, no merge kernel), 8 warps for rows below 64 K elements.
