@@ -403,7 +403,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")   # keep NCCL's version banner off stdout: one JSON line only
+        os.environ.pop("NCCL_DEBUG", None)   # at VERSION/WARN/INFO NCCL prints a banner on stdout; this run prints one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     tpb._lib.lib()
     peak, peak_kind = measured_peak()
