@@ -255,11 +255,21 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
         total = 1 << 31
         start, stop = tpb.flat_partition(total, rank, world)
         x = gen_c4(torch, dev, gen, stop - start)
-        red = tpb.ShardedReducer(dev)
+        # two kernels per rank: slice reduction, then merge + peer-to-peer exchange of the 40-byte records +
+        # rank-ordered merge (falls back to kernel -> NCCL all-gather -> kernel without symmetric memory)
+        launches = 2
+        try:
+            if os.environ.get("TPB200_BENCH_NO_FUSED"):
+                raise RuntimeError("fused exchange switched off")
+            red = tpb.ShardedReducer(dev, fused=True)
+        except Exception:
+            red = tpb.ShardedReducer(dev)
+            launches = 3
+        tag = "fused P2P exchange" if launches == 2 else "all-gather"
         for op in ["sum", "mean", "var", "max", "argmax"]:
-            cases.append(Case(f"{op} whole tensor 2^31 / {world} GPUs",
+            cases.append(Case(f"{op} whole tensor 2^31 / {world} GPUs ({tag})",
                               (lambda op: (lambda i: red.reduce(op, x, start, total)))(op),
-                              (stop - start) * 4 + 8, 1, 3, [x]))
+                              (stop - start) * 4 + 8, 1, launches, [x]))
     elif workload == "c5":
         # strong scaling: the 512 rows are split in contiguous blocks, one per rank
         r0, r1 = tpb.row_block(512, rank, world)

@@ -140,6 +140,26 @@ size_t tpb200_reduce_partial_workspace_bytes(int family, int dtype, int64_t n);
 int tpb200_reduce_combine(int op, const void* partials, int n_parts, int64_t total_count,
                           int64_t correction, void* out_val, int64_t* out_idx, void* stream);
 
+/* ---- fused partial + exchange over peer memory (NVLink) ----------------------------------------
+ * No reference counterpart.  The same result as tpb200_reduce_partial -> all-gather ->
+ * tpb200_reduce_combine without a library collective: after the slice kernel, a one-warp kernel
+ * merges the slices and writes this rank's record straight into the exchange buffer of every rank
+ * (peer-to-peer stores; no multicast), raises an epoch flag and waits -- bounded -- for the flags
+ * of all ranks before merging the `world` records in rank order.
+ *   peer_buffers  host array of `world` device pointers: the exchange buffer of every rank as
+ *                 mapped on THIS GPU (peer_buffers[rank] is this rank's own); each buffer has
+ *                 tpb200_exchange_buffer_bytes() bytes and is zero-filled once before the first call
+ *   n / global_offset / total_count   this rank's flat partition and the size of the whole tensor
+ * All ranks must issue the same sequence of calls (one process per GPU, one kernel in flight per
+ * rank).  A rank whose peers never arrive gives up after a bounded wait: nothing is written and
+ * tpb200_device_status() reports it.  world <= 16.
+ */
+size_t tpb200_exchange_buffer_bytes(void);
+int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, int64_t n, int64_t global_offset,
+                                 int64_t total_count, int64_t correction, int rank, int world,
+                                 void* const* peer_buffers, void* out_val, int64_t* out_idx,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- global top-k over candidate lists --------------------------------------------------------
  * Final step of a sharded top-k: `n_cand` candidates (value, int64 GLOBAL index), e.g. the
  * all-gathered local top-k lists of every GPU, are reduced to the best k under the same order

@@ -24,7 +24,8 @@ SYMBOLS = [
     "tpb200_last_error", "tpb200_version", "tpb200_reduce", "tpb200_reduce_workspace_bytes",
     "tpb200_topk", "tpb200_topk_workspace_bytes", "tpb200_reduce_partial",
     "tpb200_reduce_partial_workspace_bytes", "tpb200_reduce_combine", "tpb200_topk_merge",
-    "tpb200_device_status", "tpb200_reduce_all_noalloc",
+    "tpb200_device_status", "tpb200_reduce_all_noalloc", "tpb200_exchange_buffer_bytes",
+    "tpb200_reduce_fused_exchange",
 ]
 
 _I64P = ctypes.POINTER(ctypes.c_int64)
@@ -71,6 +72,10 @@ def lib() -> ctypes.CDLL:
     L.tpb200_topk_merge.argtypes = [vp, vp, i64, i64, i, vp, i64, vp, vp, vp]
     L.tpb200_reduce_all_noalloc.restype = i
     L.tpb200_reduce_all_noalloc.argtypes = [i, vp, i, i64, i64, vp, vp, vp]
+    L.tpb200_exchange_buffer_bytes.restype = sz
+    L.tpb200_exchange_buffer_bytes.argtypes = []
+    L.tpb200_reduce_fused_exchange.restype = i
+    L.tpb200_reduce_fused_exchange.argtypes = [i, vp, i, i64, i64, i64, i64, i, i, ctypes.POINTER(ctypes.c_void_p), vp, vp, vp, sz, vp]
     L.tpb200_device_status.restype = i
     L.tpb200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     _lib = L

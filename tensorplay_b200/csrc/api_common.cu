@@ -31,7 +31,35 @@ int sm_count() {
     return cached[dev];
 }
 
+// Set by a kernel whose bounded wait gave up (its outputs are then not written): top-k rendezvous /
+// polling, or the peer exchange of the fused sharded reduction.  One word per device, in the
+// module's global memory; kernels get its address as a plain pointer.
+__device__ int g_device_status = 0;
+
+int* device_status_word() {
+    static std::mutex mu;
+    static int* cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return nullptr; }
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cached[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+        cached[dev] = (int*)p;
+    }
+    return cached[dev];
+}
+
 }  // namespace tpb
+
+extern "C" int tpb200_device_status(int* status_out) {
+    if (!status_out) return tpb::fail(TPB200_ERR_INVALID, "status_out is NULL");
+    int v = 0, zero = 0;
+    TPB_CUDA_OK(cudaMemcpyFromSymbol(&v, tpb::g_device_status, sizeof(int)));
+    if (v != 0) TPB_CUDA_OK(cudaMemcpyToSymbol(tpb::g_device_status, &zero, sizeof(int)));
+    *status_out = v;
+    return TPB200_OK;
+}
 
 extern "C" const char* tpb200_last_error(void) { return tpb::last_error_slot().c_str(); }
 extern "C" int tpb200_version(void) { return TPB200_VERSION; }

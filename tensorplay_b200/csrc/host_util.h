@@ -44,6 +44,7 @@ inline int cuda_fail(cudaError_t e, const char* what) {
     } while (0)
 
 int sm_count();  // SMs of the current device (148 on B200), cached per device
+int* device_status_word();  // device address of the per-device status word (nullptr without a device)
 
 inline long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 inline long long round_up(long long a, long long b) { return ceil_div(a, b) * b; }

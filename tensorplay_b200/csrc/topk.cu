@@ -584,25 +584,6 @@ topk_merge_pairs_kernel(const float* __restrict__ cv, const long long* __restric
     }
 }
 
-// ------------------------------------------------------------------ device status ----------
-// Set to 1 by a kernel whose bounded wait on a bulk copy gave up (its outputs are then not
-// written).  One word per device, lives in the module's global memory.
-__device__ int g_device_status = 0;
-
-static int* device_status_word() {
-    static std::mutex mu;
-    static int* cached[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return nullptr; }
-    std::lock_guard<std::mutex> lk(mu);
-    if (!cached[dev]) {
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
-        cached[dev] = (int*)p;
-    }
-    return cached[dev];
-}
-
 // ------------------------------------------------------------------ planner ----------------
 enum TopkPath { TK_NONE, TK_SORTROW, TK_STREAM };
 
@@ -825,14 +806,5 @@ extern "C" int tpb200_topk_merge(const float* cand_val, const int64_t* cand_idx,
         topk_merge_pairs_kernel<false><<<1, threads, sm, st>>>(cand_val, (const long long*)cand_idx, (int)n_cand, N, (int)k, lo, ll, out_val, (long long*)out_idx);
     }
     TPB_LAUNCH_OK("topk_merge_pairs_kernel");
-    return TPB200_OK;
-}
-
-extern "C" int tpb200_device_status(int* status_out) {
-    if (!status_out) return fail(TPB200_ERR_INVALID, "status_out is NULL");
-    int v = 0, zero = 0;
-    TPB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
-    if (v != 0) TPB_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
-    *status_out = v;
     return TPB200_OK;
 }

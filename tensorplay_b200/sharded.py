@@ -70,6 +70,18 @@ class _CudaBackend:
         _lib.check(self.lib.tpb200_reduce_partial(fam, x.data_ptr() if n else None, _lib.F32, n, offset,
                                                   slot.data_ptr(), ws, wsn, self.stream()))
 
+    def fused(self, op: str, x: torch.Tensor, offset: int, total: int, correction: int, rank: int, world: int,
+              peer_ptrs, out_val, out_idx) -> None:
+        import ctypes
+        n = x.numel()
+        fam = _lib.OP[op]
+        ws, wsn = self.workspace(self.lib.tpb200_reduce_partial_workspace_bytes(fam, _lib.F32, n))
+        arr = (ctypes.c_void_p * world)(*peer_ptrs)
+        _lib.check(self.lib.tpb200_reduce_fused_exchange(
+            fam, x.data_ptr() if n else None, _lib.F32, n, offset, total, correction, rank, world, arr,
+            out_val.data_ptr() if out_val is not None else None,
+            out_idx.data_ptr() if out_idx is not None else None, ws, wsn, self.stream()))
+
     def combine(self, op: str, records: torch.Tensor, n_parts: int, total: int, correction: int,
                 out_val, out_idx) -> None:
         _lib.check(self.lib.tpb200_reduce_combine(
@@ -100,7 +112,7 @@ class ShardedReducer:
     no other product backend.
     """
 
-    def __init__(self, device: torch.device | None = None, group=None, backend=None):
+    def __init__(self, device: torch.device | None = None, group=None, backend=None, fused: bool = False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -115,6 +127,27 @@ class ShardedReducer:
         self.out_val = torch.empty(1, dtype=torch.float32, device=self.device)
         self.out_idx = torch.empty(1, dtype=torch.int64, device=self.device)
         self._cand = {}
+        # fused = True: whole-tensor reductions exchange their records inside the reduction kernel,
+        # by peer-to-peer stores into symmetric memory (NVLink), instead of an NCCL all-gather
+        self.peer_ptrs = None
+        if fused:
+            self._setup_exchange()
+
+    def _setup_exchange(self) -> None:
+        nbytes = self.backend.lib.tpb200_exchange_buffer_bytes()
+        if self.world == 1:
+            self._xbuf = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            self.peer_ptrs = [self._xbuf.data_ptr()]
+            return
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer mappings only
+        import torch.distributed._symmetric_memory as symm_mem
+        self._xbuf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self._xhdl = symm_mem.rendezvous(self._xbuf, self.group if self.group is not None else dist.group.WORLD)
+        self._xbuf.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self.peer_ptrs = [int(p) for p in self._xhdl.buffer_ptrs]
 
     # -- whole-tensor reductions ---------------------------------------------------------
     def reduce(self, op: str, local: torch.Tensor, global_offset: int, total_count: int, correction: int = 1):
@@ -125,6 +158,13 @@ class ShardedReducer:
             raise ValueError(f"unknown reduction {op!r}")
         if local.dim() != 1 or not local.is_contiguous():
             raise ValueError("the local partition must be a contiguous 1-D tensor")
+        want_val = op not in ("argmax", "argmin")
+        want_idx = op in ("argmax", "argmin", "max_argmax", "min_argmin")
+        if self.peer_ptrs is not None:
+            self.backend.fused(op, local, int(global_offset), int(total_count), int(correction), self.rank,
+                               self.world, self.peer_ptrs, self.out_val if want_val else None,
+                               self.out_idx if want_idx else None)
+            return (self.out_val if want_val else None), (self.out_idx if want_idx else None)
         self.backend.partial(_FAMILY[op], local, int(global_offset), self.records[self.rank])
         if self.world > 1:
             dist.all_gather_into_tensor(self.records.view(-1), self.records[self.rank], group=self.group)

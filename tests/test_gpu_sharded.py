@@ -102,6 +102,29 @@ def test_sharded_reducer_one_rank(cuda):
     assert ti.tolist() == list(range((1 << 20) - 1, (1 << 20) - 9, -1))
 
 
+def test_fused_exchange_one_rank(cuda):
+    """The fused kernel with a single rank exchanges with itself: ticket, epoch and parity logic over
+    several calls in a row, bit-identical to the unfused path."""
+    import torch
+    import tensorplay_b200 as tpb
+    from util import config4
+    x = torch.from_numpy(config4(n=(1 << 22) + 77)).to(cuda)
+    plain = tpb.ShardedReducer(cuda)
+    fused = tpb.ShardedReducer(cuda, fused=True)
+    for rep in range(3):
+        for op in ("sum", "mean", "var", "std", "max", "argmax", "min_argmin"):
+            pv, pi = plain.reduce(op, x, 0, x.numel())
+            pv = None if pv is None else pv.clone()
+            pi = None if pi is None else pi.clone()
+            fv, fi = fused.reduce(op, x, 0, x.numel())
+            if pv is not None:
+                assert torch.equal(pv.view(torch.int32), fv.view(torch.int32)), (rep, op)
+            if pi is not None:
+                assert torch.equal(pi, fi), (rep, op)
+    from tensorplay_b200 import _lib
+    assert _lib.device_status() == 0
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -134,6 +157,15 @@ def _nccl_worker(rank, world, port, ret):
             out[op] = (None if v is None else float(v.item()), None if i is None else int(i.item()))
         tv, ti = red.topk(local, 32, a, True)
         out["topk"] = ti.tolist()
+        # the fused peer-to-peer exchange must give bit-identical results, call after call
+        fused = tpb.ShardedReducer(dev, fused=True)
+        for rep in range(3):
+            for op in ("sum", "var", "max_argmax", "argmin"):
+                v, i = fused.reduce(op, local, a, n)
+                got = (None if v is None else float(v.item()), None if i is None else int(i.item()))
+                assert got == out[op], (rank, rep, op, got, out[op])
+        from tensorplay_b200 import _lib
+        assert _lib.device_status() == 0
         ret[rank] = out
     finally:
         dist.destroy_process_group()
