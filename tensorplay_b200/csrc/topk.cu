@@ -8,15 +8,17 @@
 // +0.0; NaN -> 0).  Larger word = earlier in the output.  All words of a row are distinct, so
 // "top k by rank word" IS the stable order including its tie rule -- no separate tie pass.
 //
-// One HBM pass.  A row (or a fixed slice of it) is streamed once by one CTA in tiles of
-// 512 threads x 4 x float4.  The CTA keeps a candidate buffer of rank words in shared memory
-// and an exclusive threshold tau: an element is a candidate iff its word > tau.  On the hot
-// path that test is ONE float compare per element (x > value(tau)): within a CTA indices only
-// grow, so an element equal to the threshold value always loses its tie.  tau starts from the
-// k-th largest of per-thread group maxima of the first tile (a valid lower bound of the k-th
-// best) and rises every time the buffer fills and is cut back to its k best (bitonic sort in
-// shared memory).  Rows shorter than a few tiles are sorted whole in shared memory instead;
-// rows split over several CTAs are merged by a second, tiny kernel.
+// One HBM pass.  A row (or a fixed slice of it) is streamed once by one CTA, every warp on its own
+// 1024-element tiles.  The CTA keeps candidate rank words in shared memory and an exclusive
+// threshold tau: an element is a candidate iff its word > tau.  On the hot path that test is ONE
+// float compare per element (x >= value(tau); the exact 64-bit compare is only made for the few
+// that pass).  tau starts from the k-th largest of a sample of lane maxima of the first tiles (a
+// k-th largest of any subset of the row is a valid lower bound of the k-th best) and rises every
+// time candidates are cut back to their k best.  Two streaming kernels share this scheme:
+// topk_smallk_kernel (k <= 64: a ring of candidates cut 64 words at a time by single warps, no
+// barrier while streaming) and topk_stream_kernel (k <= 2048: a buffer cut by the whole CTA at a
+// rendezvous).  Rows of at most 4096 elements are sorted whole in shared memory instead; rows
+// split over several CTAs are merged by a second, tiny kernel.
 #include "common.cuh"
 #include "host_util.h"
 
@@ -505,6 +507,334 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     }
 }
 
+// ------------------------------------------------------------------ small-k streaming kernel
+// k <= 64.  Same one-pass idea as topk_stream_kernel, but after the bootstrap NO barrier of the CTA
+// is left, candidates never go back to memory, and a cut never stops the other warps:
+//  * the warps take 1024-element tiles from a shared counter;
+//  * the threshold test is one float compare per element and leaves a 32-bit mask per lane; the few
+//    elements that pass are read again by address (an L2 hit), ranked exactly (64-bit word) and
+//    appended, one shared-memory atomic each, to a RING of 1024 words whose write position only grows;
+//  * the ring is consumed in chunks of 64 words.  The warp whose reservation completes chunk c cuts
+//    it: it waits (bounded) for chunk c-1 to be done and for the 64 slots to be written (an empty
+//    slot is 0, a rank word never is), sorts them together with the 64 survivors of the earlier
+//    chunks in registers (128 words, four per lane, about a microsecond), leaves the best 64 as
+//    the new survivors, raises the threshold to the k-th of them, zeroes the slots and advances
+//    `consumed`.  Meanwhile the other warps stream on; they only wait if the ring is full, i.e. if
+//    the cuts are 15 chunks behind;
+//  * the warp that leaves last merges the unfinished chunk with the survivors and writes the output.
+// A lane whose reservation completes a chunk, or finds the ring full, stops appending; the warp
+// then handles these events in ascending ring position (write the word once there is room, cut the
+// chunk) before any lane reserves again.  Waits therefore only ever depend on lower positions and
+// cannot form a cycle; every wait is bounded all the same and ends with a code in the status word
+// and unwritten outputs.
+constexpr int kSmallK = 64;
+constexpr int kRing = 1024;
+constexpr int kChunk = 64;
+constexpr int kSmallSpin = 1 << 22;
+enum { kErrSlot = 6, kErrRingFull = 7, kErrChunkOrder = 8 };
+
+struct SmallShared {
+    unsigned long long tau;        // exclusive threshold, only ever raised
+    unsigned long long best[64];   // survivors of the chunks cut so far, sorted descending, 0-padded
+    unsigned bootk[128];           // bootstrap: the warps' largest lane maxima (as keys)
+    unsigned cnt;                  // words ever reserved in the ring
+    unsigned consumed;             // words taken over by cuts
+    int next;                      // next warp-tile of the slice
+    int done;                      // warps that have left the streaming loop
+    int err;
+};
+
+// Bounded wait for a ring slot to be written; 0 on give-up.
+__device__ __forceinline__ unsigned long long wait_slot(const unsigned long long* p, const int* err) {
+    unsigned long long w = *(const volatile unsigned long long*)p;
+    for (int spin = 0; w == 0ull && spin < kSmallSpin; ++spin) {
+        if (*(const volatile int*)err) break;
+        __nanosleep(20);
+        w = *(const volatile unsigned long long*)p;
+    }
+    return w;
+}
+
+__device__ __forceinline__ void small_give_up(SmallShared* sh, int* status, int code, int lane) {
+    if (lane == 0) {
+        *(volatile int*)&sh->err = code;
+        if (status) atomicMax(status, code);
+    }
+}
+
+// Warp-uniform bounded wait until `consumed` has reached `target`; false on give-up.
+__device__ __noinline__ bool wait_consumed(SmallShared* sh, unsigned target, int lane) {
+    int ok = 0;
+    if (lane == 0) {
+        for (int spin = 0; spin < kSmallSpin; ++spin) {
+            if (*(volatile unsigned*)&sh->consumed >= target) { ok = 1; break; }
+            if (*(volatile int*)&sh->err) break;
+            __nanosleep(40);
+        }
+    }
+    return __shfl_sync(kFull, ok, 0) != 0;
+}
+
+// Cut chunk c of the ring (called by one whole warp).  n_new = words of the chunk (kChunk, or
+// fewer for the unfinished chunk at the end).  Leaves the sorted union's best 64 in sh->best;
+// false on give-up.
+__device__ __noinline__ bool cut_chunk(unsigned long long* ring, SmallShared* sh, unsigned c, int n_new, int k,
+                                       int lane, int* status) {
+    unsigned long long v[4];
+    if (!wait_consumed(sh, c * kChunk, lane)) { small_give_up(sh, status, kErrChunkOrder, lane); return false; }
+    bool ok = true;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int i = lane * 2 + e;
+        v[e] = 0ull;
+        if (i < n_new) {
+            unsigned long long* slot = &ring[(c * kChunk + i) & (kRing - 1)];
+            v[e] = wait_slot(slot, &sh->err);
+            ok &= v[e] != 0ull;
+            *(volatile unsigned long long*)slot = 0ull;
+        }
+    }
+    v[2] = sh->best[lane * 2];
+    v[3] = sh->best[lane * 2 + 1];
+    if (!__all_sync(kFull, ok)) { small_give_up(sh, status, kErrSlot, lane); return false; }
+    warp_sort_desc<4>(v, lane);
+    if (lane < 16) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sh->best[lane * 4 + e] = v[e];
+    }
+    unsigned long long sel = v[0];
+#pragma unroll
+    for (int e = 1; e < 4; ++e) sel = ((k - 1) & 3) == e ? v[e] : sel;
+    const unsigned long long kth = __shfl_sync(kFull, sel, (k - 1) >> 2);
+    __syncwarp();
+    if (lane == 0) {
+        // fewer than k words so far (kth == 0) leaves the threshold alone
+        if (kth != 0ull && kth - 1ull > *(volatile unsigned long long*)&sh->tau) *(volatile unsigned long long*)&sh->tau = kth - 1ull;
+        __threadfence_block();
+        *(volatile unsigned*)&sh->consumed = c * kChunk + n_new;
+    }
+    __syncwarp();
+    return true;
+}
+
+template <bool LARGEST, bool VEC, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == 4 ? 7 : (NW == 8 ? 4 : 2))
+topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
+                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
+    __shared__ __align__(16) unsigned long long ring[kRing];
+    __shared__ SmallShared sh;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int s = blockIdx.x;
+    const long long r = blockIdx.y;
+    const float* row = topk_row(in, g, r);
+    const long long begin = (long long)s * g.chunk;
+    long long len = g.len - begin;
+    if (len > g.chunk) len = g.chunk;
+    const float* slice = row + begin * g.es;
+    const int ntiles = (int)((len + kWarpTile - 1) / kWarpTile);
+    const int k = (int)g.k;
+
+    for (int i = tid; i < kRing; i += NW * 32) ring[i] = 0ull;
+    if (tid < 64) sh.best[tid] = 0ull;
+    if (tid == 0) { sh.tau = 0ull; sh.cnt = 0u; sh.consumed = 0u; sh.next = NW; sh.done = 0; sh.err = 0; }
+
+    // Element j (0..31) of this lane in the tile at offset `off`: float4 number u*32+lane, component
+    // c, j = 4u+c.
+    auto elem_off = [&](long long off, int j) -> long long { return off + ((j >> 2) * 32 + lane) * 4 + (j & 3); };
+
+    // A tile in registers.  Elements past the end of the slice read as NaN.
+    auto load_tile = [&](float4 (&v)[8], long long off) {
+        if (VEC && off + kWarpTile <= len) {
+            const float* p = slice + off + lane * 4;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = ld_stream4(p + u * 128);
+        } else {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const long long e0 = off + (u * 32 + lane) * 4;
+                float t[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) t[c] = e0 + c < len ? ld_stream1(slice + (e0 + c) * g.es) : NAN;
+                v[u] = make_float4(t[0], t[1], t[2], t[3]);
+            }
+        }
+    };
+
+    // Bit j set: element j of this lane may beat the threshold.  The float test lets ties with the
+    // threshold value pass (a tie with a lower index outranks it); the exact compare decides later.
+    auto mask_of = [&](const float4 (&v)[8], unsigned long long tau) -> unsigned {
+        if ((tau >> 32) == 0ull) return 0xffffffffu;   // the threshold's key is 0 (NaN rank): rank everything
+        const float tvf = key_value<LARGEST>((unsigned)(tau >> 32));
+        unsigned m = 0u;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const bool p0 = LARGEST ? (v[u].x >= tvf) : (v[u].x <= tvf);
+            const bool p1 = LARGEST ? (v[u].y >= tvf) : (v[u].y <= tvf);
+            const bool p2 = LARGEST ? (v[u].z >= tvf) : (v[u].z <= tvf);
+            const bool p3 = LARGEST ? (v[u].w >= tvf) : (v[u].w <= tvf);
+            m |= (p0 ? 1u : 0u) << (4 * u) | (p1 ? 2u : 0u) << (4 * u) | (p2 ? 4u : 0u) << (4 * u) |
+                 (p3 ? 8u : 0u) << (4 * u);
+        }
+        return m;
+    };
+
+    // Append the masked elements of the tile at `off`; false after a give-up.
+    auto drain = [&](unsigned m, long long off) -> bool {
+        for (int pass = 0; __any_sync(kFull, m != 0u); ++pass) {
+            if (pass > (1 << 22)) { small_give_up(&sh, status, kErrRetry, lane); return false; }
+            const unsigned long long tnow = *(volatile unsigned long long*)&sh.tau;
+            unsigned ev_pos = 0xffffffffu;     // a reservation of this lane that the warp must attend to
+            unsigned long long ev_w = 0ull;
+            int ev_kind = 0;                   // 1: not written yet, the ring was full;  2: completes a chunk
+            while (m != 0u) {
+                const int j = __ffs(m) - 1;
+                m &= m - 1u;
+                const long long e = elem_off(off, j);
+                if (e < len) {
+                    const float xv = slice[e * g.es];
+                    const unsigned long long w = rank_word<LARGEST>(xv, (unsigned)(begin + e));
+                    if (w > tnow) {
+                        const unsigned pos = atomicAdd(&sh.cnt, 1u);
+                        const bool full = pos - *(volatile unsigned*)&sh.consumed >= (unsigned)kRing;
+                        if (!full) *(volatile unsigned long long*)&ring[pos & (kRing - 1)] = w;
+                        const bool duty = (pos + 1u) % (unsigned)kChunk == 0u;
+                        if (full || duty) {
+                            ev_pos = pos; ev_w = w; ev_kind = (full ? 1 : 0) | (duty ? 2 : 0);
+                            break;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            for (;;) {   // events of the warp in ascending ring position (rare)
+                const unsigned pmin = __reduce_min_sync(kFull, ev_pos);
+                if (pmin == 0xffffffffu) break;
+                const bool mine = ev_pos == pmin;
+                const int src = __ffs(__ballot_sync(kFull, mine)) - 1;
+                const int kind = __shfl_sync(kFull, ev_kind, src);
+                if (kind & 1) {
+                    if (!wait_consumed(&sh, pmin - (unsigned)kRing + 1u, lane)) { small_give_up(&sh, status, kErrRingFull, lane); return false; }
+                    if (mine) *(volatile unsigned long long*)&ring[pmin & (kRing - 1)] = ev_w;
+                    __syncwarp();
+                }
+                if (kind & 2) {
+                    if (!cut_chunk(ring, &sh, pmin / (unsigned)kChunk, kChunk, k, lane, status)) return false;
+                }
+                if (mine) ev_pos = 0xffffffffu;
+            }
+        }
+        return true;
+    };
+
+    // ---- bootstrap: warp w loads tile w and sorts its 32 lane maxima (as keys) with shuffles; the
+    // 128/NW largest of every warp are put together and the k-th largest of those 128 -- found by
+    // rank counting, one thread per key -- is the first threshold.  All 128 are distinct elements of
+    // the row, so at least k elements reach it; it is almost always within a few ranks of the
+    // exact k-th largest of the first NW*1024 elements.  (The planner guarantees len >= NW tiles.)
+    bool failed = false;
+    {
+        float4 v[8];
+        const long long off = (long long)warp * kWarpTile;
+        load_tile(v, off);
+        float mx = NAN;   // fmaxf/fminf ignore a NaN operand: stays NaN only if the lane saw nothing else
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (LARGEST) mx = fmaxf(fmaxf(mx, v[u].x), fmaxf(fmaxf(v[u].y, v[u].z), v[u].w));
+            else         mx = fminf(fminf(mx, v[u].x), fminf(fminf(v[u].y, v[u].z), v[u].w));
+        }
+        unsigned key = rank_key<LARGEST>(mx);
+#pragma unroll
+        for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                const unsigned o = __shfl_xor_sync(kFull, key, stride);
+                const bool keep_max = ((lane & stride) == 0) == ((lane & size) == 0);
+                key = keep_max ? (o > key ? o : key) : (o < key ? o : key);
+            }
+        }
+        constexpr int kShare = 128 / NW;
+        if (lane < kShare) sh.bootk[warp * kShare + lane] = key;
+        __syncthreads();
+        if (tid < 128) {
+            const unsigned my = sh.bootk[tid];
+            int above = 0, equal = 0;
+            for (int i = 0; i < 128; ++i) {
+                const unsigned o = sh.bootk[i];
+                above += o > my ? 1 : 0;
+                equal += o == my ? 1 : 0;
+            }
+            if (above < k && k <= above + equal) sh.tau = (unsigned long long)my << 32;   // same value from every writer
+        }
+        __syncthreads();
+        const unsigned m = mask_of(v, *(volatile unsigned long long*)&sh.tau);
+        if (!drain(m, off)) failed = true;
+    }
+
+    // ---- streaming loop: no barrier, tiles from a shared counter
+    while (!failed) {
+        int t = 0;
+        unsigned long long tau = 0ull;
+        if (lane == 0) {
+            t = atomicAdd(&sh.next, 1);
+            tau = *(volatile unsigned long long*)&sh.tau;
+            if (*(volatile int*)&sh.err) t = ntiles;
+        }
+        t = __shfl_sync(kFull, t, 0);
+        tau = __shfl_sync(kFull, tau, 0);
+        if (t >= ntiles) break;
+        const long long off = (long long)t * kWarpTile;
+        unsigned m;
+        {
+            float4 v[8];
+            load_tile(v, off);
+            m = mask_of(v, tau);
+        }
+        if (!drain(m, off)) failed = true;
+    }
+
+    // ---- the warp that leaves last merges the unfinished chunk with the survivors and writes the output
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+        __threadfence_block();
+        last = atomicAdd(&sh.done, 1) == NW - 1;
+    }
+    last = __shfl_sync(kFull, last, 0);
+    if (!last) return;
+    if (*(volatile int*)&sh.err) {
+        if (lane == 0 && status) atomicMax(status, 1);
+        return;   // outputs stay unwritten; the host reads the status word
+    }
+    const unsigned total = *(volatile unsigned*)&sh.cnt;
+    const unsigned c_last = total / (unsigned)kChunk;    // every complete chunk has been cut by its warp
+    const int n_new = (int)(total - c_last * (unsigned)kChunk);
+    if (!wait_consumed(&sh, c_last * (unsigned)kChunk, lane)) {
+        small_give_up(&sh, status, kErrChunkOrder, lane);
+        return;
+    }
+    auto emit = [&](unsigned long long w, int rank) {
+        if (w == 0ull || rank >= k) return;
+        if (ws) {
+            ws[((size_t)r * g.S + s) * (size_t)k + rank] = w;
+        } else {
+            const unsigned idx = word_index(w);
+            const unsigned key = (unsigned)(w >> 32);
+            float val = key_value<LARGEST>(key);
+            // the key folds -0.0 onto +0.0 and all NaNs onto one rank: those come from the row
+            if (key == 0u || val == 0.0f) val = row[(long long)idx * g.es];
+            out_idx[r * k + rank] = (long long)idx;
+            out_val[r * k + rank] = val;
+        }
+    };
+    if (!cut_chunk(ring, &sh, c_last, n_new, k, lane, status)) {
+        if (lane == 0 && status) atomicMax(status, 1);
+        return;
+    }
+    __syncwarp();
+    emit(sh.best[lane * 2], lane * 2);
+    emit(sh.best[lane * 2 + 1], lane * 2 + 1);
+}
+
 // ------------------------------------------------------------------ sort kernels -----------
 // FROM_ROW: rank every element of a short row.  Otherwise: merge the S*k slice survivors of a row.
 // One CTA per row, whole working set in shared memory.
@@ -585,7 +915,7 @@ topk_merge_pairs_kernel(const float* __restrict__ cv, const long long* __restric
 }
 
 // ------------------------------------------------------------------ planner ----------------
-enum TopkPath { TK_NONE, TK_SORTROW, TK_STREAM };
+enum TopkPath { TK_NONE, TK_SORTROW, TK_STREAM, TK_SMALLK };
 
 struct TopkPlan {
     TopkPath path = TK_NONE;
@@ -665,6 +995,38 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
         // grid.y limit; such shapes have short rows in practice
         return fail(TPB200_ERR_UNSUPPORTED, "more than 65535 rows of more than 4096 elements are not supported");
     }
+    const int sms = sm_count();
+    const char* fsk = getenv("TPB200_TOPK_SMALLK");   // "0": experiments with the general kernel
+    if (k <= kSmallK && !(fsk && atoi(fsk) == 0)) {
+        // barrier-free ring kernel.  CTA width: 16 warps for long rows (one bootstrap and one final
+        // step per row, no merge kernel; measured on [256,151936], k = 50: 30.4 us against 38.3 us
+        // for 8 warps, 39.5 us for two 8-warp slices and 48.1 us for four 4-warp slices per row),
+        // narrower CTAs for short rows; slices only where the rows alone cannot fill the GPU
+        pl->path = TK_SMALLK;
+        g.B = kRing;
+        g.soft = kChunk;
+        g.warps = len >= 64 * 1024 ? 16 : (len >= 16 * 1024 ? 8 : 4);
+        if (const char* fw = getenv("TPB200_TOPK_WARPS")) { int w = atoi(fw); g.warps = w == 16 ? 16 : (w == 8 ? 8 : 4); }   // experiments
+        const int per_sm = g.warps == 4 ? 7 : (g.warps == 8 ? 4 : 2);
+        long long want = std::max(1LL, (long long)sms * per_sm / rows);
+        long long most = std::max(1LL, len / (8LL * g.warps * kWarpTile));
+        long long S = std::min(want, most);
+        if (const char* fs = getenv("TPB200_TOPK_SLICES")) S = std::max(1LL, std::min((long long)atoi(fs), len / ((long long)g.warps * kWarpTile)));
+        g.chunk = round_up(ceil_div(len, S), 4);
+        g.S = (int)ceil_div(len, g.chunk);
+        // the last slice must still hold one tile per warp for the bootstrap
+        while (g.S > 1 && len - (long long)(g.S - 1) * g.chunk < (long long)g.warps * kWarpTile) {
+            --S;
+            g.chunk = round_up(ceil_div(len, S), 4);
+            g.S = (int)ceil_div(len, g.chunk);
+        }
+        if (len < (long long)g.warps * kWarpTile) { g.warps = 4; }   // len > 4096 here, so four tiles exist
+        if (g.S > 1) {
+            pl->mergeN = std::max(2, pow2_ceil((long long)g.S * k));
+            pl->ws_bytes = (size_t)rows * g.S * k * sizeof(unsigned long long);
+        }
+        return TPB200_OK;
+    }
     pl->path = TK_STREAM;
     g.B = pow2_ceil(std::max<long long>(4 * k, 1024));
     // first cut early: handling a candidate costs far more than skipping an element, and only a cut
@@ -672,7 +1034,6 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     g.soft = (int)std::min<long long>(g.B / 2, std::max<long long>(320, 3 * k));
     if (const char* fb = getenv("TPB200_TOPK_B")) g.B = std::max(g.B, pow2_ceil(atoi(fb)));                        // experiments
     if (const char* fso = getenv("TPB200_TOPK_SOFT")) g.soft = std::min(g.B - 1, std::max(atoi(fso), (int)k + 1));   // experiments
-    const int sms = sm_count();
     // CTA width: 16 warps for long rows (half as many bootstraps / cuts as two 8-warp slices and,
     // with one CTA per row, no merge kernel), 8 warps for rows below 64 K elements.
     g.warps = len >= 64 * 1024 ? 16 : 8;
@@ -723,8 +1084,18 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
     dim3 grid((unsigned)g.S, (unsigned)g.rows);
     unsigned long long* w = g.S > 1 ? (unsigned long long*)ws : nullptr;
     int* status = device_status_word();
-    const size_t sm = (size_t)g.B * 12;
     const int threads = g.warps * 32;
+    if (pl.path == TK_SMALLK) {
+#define TPB_LAUNCH_SMALLK(V, W) topk_smallk_kernel<LARGEST, V, W><<<grid, threads, 0, st>>>(in, g, w, ov, oi, status)
+        if (pl.vec) {
+            if (g.warps == 16) TPB_LAUNCH_SMALLK(true, 16); else if (g.warps == 8) TPB_LAUNCH_SMALLK(true, 8); else TPB_LAUNCH_SMALLK(true, 4);
+        } else {
+            if (g.warps == 16) TPB_LAUNCH_SMALLK(false, 16); else if (g.warps == 8) TPB_LAUNCH_SMALLK(false, 8); else TPB_LAUNCH_SMALLK(false, 4);
+        }
+#undef TPB_LAUNCH_SMALLK
+        TPB_LAUNCH_OK("topk_smallk_kernel");
+    } else {
+    const size_t sm = (size_t)g.B * 12;
 #define TPB_LAUNCH_STREAM(V, W)                                                                          \
     do {                                                                                                 \
         int rc = allow_smem(topk_stream_kernel<LARGEST, V, W>, sm);                                      \
@@ -735,6 +1106,7 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
     else        { if (g.warps == 16) TPB_LAUNCH_STREAM(false, 16); else TPB_LAUNCH_STREAM(false, 8); }
 #undef TPB_LAUNCH_STREAM
     TPB_LAUNCH_OK("topk_stream_kernel");
+    }
     if (g.S > 1) {
         size_t msm = (size_t)pl.mergeN * 8;
         int rc = allow_smem(topk_sort_kernel<LARGEST, false>, msm);

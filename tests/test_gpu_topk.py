@@ -128,6 +128,33 @@ def test_other_dims_and_views(cuda):
         assert_bits_equal(v.cpu().numpy(), wv)
 
 
+@pytest.mark.parametrize("warps,slices", [("4", "1"), ("4", "3"), ("8", "2"), ("16", "1")])
+def test_small_k_kernel_geometries(cuda, warps, slices, monkeypatch):
+    """k <= 64 runs the barrier-free ring kernel; every CTA width and a row split give the same
+    bit-exact answer, and no device-side wait gives up."""
+    from tensorplay_b200 import _lib
+    monkeypatch.setenv("TPB200_TOPK_WARPS", warps)
+    monkeypatch.setenv("TPB200_TOPK_SLICES", slices)
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((3, 70001)).astype(np.float32)
+    x[0, ::5] = 3.0                                   # 14001 ties above the threshold: chunk after chunk is cut
+    x[1, 60000:] = np.nan
+    x[2] = np.sort(x[2])                              # ascending: every element beats the threshold
+    for k in (1, 8, 33, 64):
+        check_topk(cuda, x, k, -1, True, what=f"warps={warps} S={slices}")
+        check_topk(cuda, x, k, -1, False, what=f"warps={warps} S={slices}")
+    nan_rows = np.full((2, 50000), np.nan, dtype=np.float32)   # fewer numbers than k: NaNs fill up by index
+    nan_rows[:, 7] = 1.0
+    nan_rows[:, 49999] = -2.0
+    check_topk(cuda, nan_rows, 40, -1, True)
+    check_topk(cuda, nan_rows, 40, -1, False)
+    zeros = np.zeros((2, 30000), dtype=np.float32)              # the sign of zero must come back bit-exact
+    zeros[:, 1::2] = -0.0
+    check_topk(cuda, zeros, 16, -1, True)
+    check_topk(cuda, zeros, 16, -1, False)
+    assert _lib.device_status() == 0
+
+
 def test_errors(cuda):
     import torch
     import tensorplay_b200 as tpb
