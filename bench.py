@@ -466,7 +466,7 @@ def main():
     line["roofline"] = {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                         "frac": round(per_gpu / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
-                        "kernel": "topk_stream_kernel" if args.workload in ("c2", "c5") else case.name,
+                        "kernel": {"c2": "topk_smallk_kernel", "c5": "topk_stream_kernel"}.get(args.workload, case.name),
                         "algorithmic_bytes_per_launch": case.alg_bytes}
 
     # end to end (host buffers) for the headline

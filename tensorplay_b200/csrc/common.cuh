@@ -98,6 +98,10 @@ struct SumAcc {
     double s;
     __device__ __forceinline__ void init() { s = 0.0; }
     __device__ __forceinline__ void add(float x, long long) { s += (double)x; }
+    // four elements at positions pos, pos + step, ...
+    __device__ __forceinline__ void add4(float x0, float x1, float x2, float x3, long long pos, long long step) {
+        add(x0, pos); add(x1, pos + step); add(x2, pos + 2 * step); add(x3, pos + 3 * step);
+    }
     __device__ __forceinline__ void finish_thread() {}
     __device__ __forceinline__ void merge(const SumAcc& o) { s += o.s; }
     __device__ __forceinline__ SumAcc shfl_down(int d) const {
@@ -107,29 +111,40 @@ struct SumAcc {
     __device__ __forceinline__ void load(const Packed* p) { s = p->d0; }
 };
 
-// Variance.  Inside one thread: moments of (x - K) in fp64, K = the thread's first element
-// (shifted-data form: no per-element division).  finish_thread() turns that into a Welford
-// triple (count, mean, M2); everything above a thread -- lanes, warps, CTAs, slices, GPUs --
-// is combined with Chan's pairwise update, always in a fixed order.
+// Variance.  Inside one thread: moments of d = x - K, K = the thread's first element (shifted-data
+// form: no per-element division, and an offset common to the data is gone before anything is
+// squared; d is exact in fp32 whenever x and K are within a factor of two of each other).  The
+// streaming loops hand over four elements at a time: their d and d*d are summed in fp32 and then
+// added to fp64 totals, so the fp64 pipe -- which bounded this kernel when every element went
+// through it -- sees a quarter of the work; a sum of four fp32 terms carries a relative error of
+// about 1e-7, inside the 1e-5 that the result is held to.  finish_thread() turns the totals into a
+// Welford triple (count, mean, M2); everything above a thread -- lanes, warps, CTAs, slices, GPUs
+// -- is combined with Chan's pairwise update in fp64, always in a fixed order.
 struct MomAcc {
-    double n, mean, m2;   // after finish_thread(): count, mean, M2
-    double k;             // before: shift; c = count, mean = sum(x-k), m2 = sum((x-k)^2)
-    unsigned int c;
-    __device__ __forceinline__ void init() { n = 0.0; mean = 0.0; m2 = 0.0; k = 0.0; c = 0u; }
+    double n, mean, m2;   // after finish_thread(): count, mean, M2;  before: mean = sum d, m2 = sum d*d
+    float kf;             // shift
+    unsigned int c;       // elements seen by this thread
+    __device__ __forceinline__ void init() { n = 0.0; mean = 0.0; m2 = 0.0; kf = 0.0f; c = 0u; }
     __device__ __forceinline__ void add(float x, long long) {
-        double xd = (double)x;
-        if (c == 0u) k = xd;
-        double d = xd - k;
+        if (c == 0u) kf = x;
+        const double d = (double)(x - kf);
         ++c;
         mean += d;
         m2 = fma(d, d, m2);
     }
+    __device__ __forceinline__ void add4(float x0, float x1, float x2, float x3, long long, long long) {
+        if (c == 0u) kf = x0;
+        c += 4u;
+        const float d0 = x0 - kf, d1 = x1 - kf, d2 = x2 - kf, d3 = x3 - kf;
+        mean += (double)((d0 + d1) + (d2 + d3));
+        m2 += (double)fmaf(d3, d3, fmaf(d2, d2, fmaf(d1, d1, d0 * d0)));
+    }
     __device__ __forceinline__ void finish_thread() {
         n = (double)c;
         if (c > 0u) {
-            const double inv = 1.0 / n;
             const double s1 = mean;
-            mean = fma(s1, inv, k);
+            const double inv = 1.0 / n;
+            mean = fma(s1, inv, (double)kf);
             m2 = m2 - s1 * s1 * inv;
             if (m2 < 0.0) m2 = 0.0;
         }
@@ -157,12 +172,12 @@ struct MomAcc {
         r.n = __shfl_down_sync(kFull, n, d);
         r.mean = __shfl_down_sync(kFull, mean, d);
         r.m2 = __shfl_down_sync(kFull, m2, d);
-        r.k = 0.0;
+        r.kf = 0.0f;
         r.c = 0u;
         return r;
     }
     __device__ __forceinline__ void store(Packed* p) const { p->d0 = n; p->d1 = mean; p->d2 = m2; p->i0 = 0; p->f0 = 0; p->pad = 0; }
-    __device__ __forceinline__ void load(const Packed* p) { n = p->d0; mean = p->d1; m2 = p->d2; k = 0.0; c = 0u; }
+    __device__ __forceinline__ void load(const Packed* p) { n = p->d0; mean = p->d1; m2 = p->d2; kf = 0.0f; c = 0u; }
 };
 
 // Extremum with the reference's rule: strict compare, first occurrence wins, NaN never wins
@@ -177,6 +192,9 @@ struct ExtAcc {
     __device__ __forceinline__ void add(float x, long long pos) {
         bool better = IS_MAX ? (x > v) : (x < v);
         if (better) { v = x; i = pos; }
+    }
+    __device__ __forceinline__ void add4(float x0, float x1, float x2, float x3, long long pos, long long step) {
+        add(x0, pos); add(x1, pos + step); add(x2, pos + 2 * step); add(x3, pos + 3 * step);
     }
     __device__ __forceinline__ void finish_thread() {}
     __device__ __forceinline__ void merge(const ExtAcc& o) {
@@ -270,13 +288,13 @@ __device__ __forceinline__ void scan_contig(Acc& acc, const float* __restrict__ 
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             long long b = qpos + ((i + (long long)u * nthr) << 2);
-            acc.add(v[u].x, b); acc.add(v[u].y, b + 1); acc.add(v[u].z, b + 2); acc.add(v[u].w, b + 3);
+            acc.add4(v[u].x, v[u].y, v[u].z, v[u].w, b, 1);
         }
     }
     for (; i < nvec; i += nthr) {
         float4 v = ld_stream4(q + (i << 2));
         long long b = qpos + (i << 2);
-        acc.add(v.x, b); acc.add(v.y, b + 1); acc.add(v.z, b + 2); acc.add(v.w, b + 3);
+        acc.add4(v.x, v.y, v.z, v.w, b, 1);
     }
     const long long done = head + (nvec << 2);
     const long long tail = len - done;

@@ -52,7 +52,7 @@ __device__ __forceinline__ const float* row_base(const float* in, const RowGeom&
 
 template <class Acc>
 __device__ __forceinline__ void add4(Acc& acc, const float4& v, long long b) {
-    acc.add(v.x, b); acc.add(v.y, b + 1); acc.add(v.z, b + 2); acc.add(v.w, b + 3);
+    acc.add4(v.x, v.y, v.z, v.w, b, 1);
 }
 
 // ------------------------------------------------------------------ ROW: warp per row ------
@@ -82,7 +82,7 @@ row_warp_kernel(const float* __restrict__ in, RowGeom g, Epilogue e, float* ov, 
 // (tps x blockDim/tps) grid of threads: x walks along a run, y over runs, and loads of four
 // different runs are issued together so a thread always has 64 bytes in flight.
 template <class Acc>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, 3)
 row_cta_kernel(const float* __restrict__ in, RowGeom g, int tps, int vec_ok, Epilogue e, float* ov,
                long long* oi) {
     __shared__ Acc sm[32];
@@ -213,6 +213,13 @@ col_kernel(const float* __restrict__ in, long long o_stride, long long L, long l
                     ok[u] = ll < l1;
                     if (ok[u]) x[u] = ld_stream4(base + ll * l_stride);
                 }
+                if (ok[3]) {
+                    // four rows of each of this thread's columns at once
+                    acc[0].add4(x[0].x, x[1].x, x[2].x, x[3].x, l, ny);
+                    acc[VEC > 1 ? 1 : 0].add4(x[0].y, x[1].y, x[2].y, x[3].y, l, ny);
+                    acc[VEC > 2 ? 2 : 0].add4(x[0].z, x[1].z, x[2].z, x[3].z, l, ny);
+                    acc[VEC > 3 ? 3 : 0].add4(x[0].w, x[1].w, x[2].w, x[3].w, l, ny);
+                } else
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     long long ll = l + (long long)u * ny;
