@@ -40,7 +40,7 @@ NOMINAL_PEAK_GBS = 8000.0
 # DRAM traffic per launch of the dominant kernel from one ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum; summaries under profiles/).  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    "c2": 155_741_440 + 4_080_128,   # profiles/topk_stream_c2.md
+    "c2": 155_642_880 + 3_520_256,   # profiles/topk_smallk_c2.md
     "c1": 67_143_424 + 418_816,      # profiles/reduce_kernels.md (row_warp_kernel)
     "c3": 536_887_808 + 6_670_848,   # profiles/reduce_kernels.md (col_kernel)
 }
