@@ -227,13 +227,18 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
         xs = [gen_c1(torch, dev, gen) for _ in range(n)]
         ov = torch.empty(4096, device=dev)
         oi = torch.empty(4096, dtype=torch.int64, device=dev)
+        ob = torch.empty(4096, dtype=torch.bool, device=dev)
         inb = 4096 * 4096 * 4
         for op, fn, outb in [("sum", lambda i: tpb.sum(xs[i % n], -1, out=ov), 16384),
                              ("mean", lambda i: tpb.mean(xs[i % n], -1, out=ov), 16384),
                              ("var", lambda i: tpb.var(xs[i % n], -1, out=ov), 16384),
                              ("max", lambda i: tpb.max(xs[i % n], -1, out=ov), 16384),
                              ("argmax", lambda i: tpb.argmax(xs[i % n], -1, out=oi), 32768),
-                             ("max+argmax", lambda i: tpb.max_with_indices(xs[i % n], -1, out=(ov, oi)), 49152)]:
+                             ("max+argmax", lambda i: tpb.max_with_indices(xs[i % n], -1, out=(ov, oi)), 49152),
+                             # the other operators of the reference's registration block
+                             ("prod", lambda i: tpb.prod(xs[i % n], -1, out=ov), 16384),
+                             ("norm p=2", lambda i: tpb.norm(xs[i % n], 2.0, -1, out=ov), 16384),
+                             ("all", lambda i: tpb.all(xs[i % n], -1, out=ob), 4096)]:
             cases.append(Case(f"{op} dim=-1 [4096,4096]", fn, inb + outb, 4096, 1, xs))
     elif workload == "c3":
         a = 64
@@ -248,7 +253,9 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
                 ("max dim=1", lambda i: tpb.max(xs[0], 1, out=ov1), a * 512 * 4, a * 512, 2),
                 ("argmin dim=1", lambda i: tpb.argmin(xs[0], 1, out=oi1), a * 512 * 8, a * 512, 2),
                 ("sum dims=(0,2)", lambda i: tpb.sum(xs[0], [0, 2], out=ov2), 16384, 4096, 1),
-                ("std dims=(0,2)", lambda i: tpb.std(xs[0], [0, 2], out=ov2), 16384, 4096, 1)]:
+                ("std dims=(0,2)", lambda i: tpb.std(xs[0], [0, 2], out=ov2), 16384, 4096, 1),
+                ("norm p=2 dim=1", lambda i: tpb.norm(xs[0], 2.0, 1, out=ov1), a * 512 * 4, a * 512, 2),
+                ("prod dims=(0,2)", lambda i: tpb.prod(xs[0], [0, 2], out=ov2), 16384, 4096, 1)]:
             cases.append(Case(f"{op} [{a},4096,512]", fn, inb + outb, rows, launches, xs))
     elif workload == "c4":
         # strong scaling: the 2^31-element tensor is split in flat partitions, one per rank

@@ -61,6 +61,16 @@ extern "C" {
 #define TPB200_OP_ARGMIN 7     /* argmin                      ReductionKernels.cu:119-121 */
 #define TPB200_OP_MAX_ARGMAX 8 /* values + indices in one pass */
 #define TPB200_OP_MIN_ARGMIN 9
+/* The other operators of the same registration block (ReductionKernels.cu:256-267, 296-345,
+ * 392-408).  tpb200_reduce only; float32 in.  PROD and the norms write float32; ALL and ANY write
+ * one byte per output element (the reference's Bool tensor: 1 = true). */
+#define TPB200_OP_PROD 10         /* prod, prod.dim_IntList                                   */
+#define TPB200_OP_NORM1 11        /* norm(p = 1): sum |x|                                     */
+#define TPB200_OP_NORM2 12        /* norm(p = 2): sqrt(sum x^2)  (the one p the reference's CUDA path has) */
+#define TPB200_OP_NORM_INF 13     /* norm(p = +inf): max |x|                                  */
+#define TPB200_OP_NORM_NEG_INF 14 /* norm(p = -inf): min |x|                                  */
+#define TPB200_OP_ALL 15          /* all, all.dim: every element != 0 (NaN counts as true)    */
+#define TPB200_OP_ANY 16          /* any, any.dim                                             */
 
 #define TPB200_MAX_DIMS 8
 

@@ -24,7 +24,9 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
-OPS = {"sum": 0, "mean": 1, "var": 2, "std": 3, "max": 4, "min": 5, "argmax": 6, "argmin": 7}
+OPS = {"sum": 0, "mean": 1, "var": 2, "std": 3, "max": 4, "min": 5, "argmax": 6, "argmin": 7,
+       "prod": 8, "norm": 9, "all": 10, "any": 11}
+_MORE = ("prod", "norm", "all", "any")
 _I64P = ctypes.POINTER(ctypes.c_int64)
 _F32P = ctypes.POINTER(ctypes.c_float)
 
@@ -51,6 +53,9 @@ def lib() -> ctypes.CDLL:
         L.tpo_reduce.restype = ctypes.c_int
         L.tpo_reduce.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, _I64P, _I64P, ctypes.c_int,
                                  _I64P, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+        L.tpo_reduce_more.restype = ctypes.c_int
+        L.tpo_reduce_more.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, _I64P, _I64P, ctypes.c_int,
+                                      _I64P, ctypes.c_double, ctypes.c_void_p]
         L.tpo_out_numel.restype = ctypes.c_int64
         L.tpo_out_numel.argtypes = [ctypes.c_int, _I64P, ctypes.c_int, _I64P]
         for f in (L.tpo_topk, L.tpo_topk_sort):
@@ -73,6 +78,9 @@ def ref() -> ctypes.CDLL:
         L.tpref_reduce.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, _I64P, _I64P, ctypes.c_int,
                                    _I64P, ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
                                    ctypes.c_int64]
+        L.tpref_reduce_more.restype = ctypes.c_int
+        L.tpref_reduce_more.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, _I64P, _I64P, ctypes.c_int,
+                                        _I64P, ctypes.c_int, ctypes.c_double, ctypes.c_void_p, ctypes.c_int64]
         L.tpref_last_error.restype = ctypes.c_char_p
         _ref = L
     return _ref
@@ -114,12 +122,24 @@ def _prep(x):
     return sizes, strides
 
 
-def reduce(op: str, x: np.ndarray, dims=None, keepdim: bool = False, correction: int = 1):
-    """C restatement.  dims=None is the overload without a dim argument."""
+def reduce(op: str, x: np.ndarray, dims=None, keepdim: bool = False, correction: int = 1, p: float = 2.0):
+    """C restatement.  dims=None is the overload without a dim argument.  `p` is norm's exponent."""
     dims = _norm_dims(dims, x.ndim)
     sizes, strides = _prep(x)
     oshape = out_shape(x.shape, dims, keepdim)
     n_out = int(np.prod(oshape, dtype=np.int64)) if len(oshape) else 1
+    if op in _MORE:
+        out = np.empty(max(n_out, 1), dtype=np.uint8 if op in ("all", "any") else np.float32)
+        rc = lib().tpo_reduce_more(OPS[op], x.ctypes.data, x.ndim, _arr(sizes), _arr(strides),
+                                   -1 if dims is None else len(dims), _arr(dims or []), float(p), out.ctypes.data)
+        if rc == -2:
+            raise RuntimeError("Dimension out of range")
+        if rc == -3:
+            raise RuntimeError(("max" if p > 0 else "min") + "(): Expected reduction dim to be non-empty")
+        if rc != 0:
+            raise RuntimeError(f"tpo_reduce_more failed: {rc}")
+        out = out[:n_out].reshape(oshape)
+        return out.astype(bool) if op in ("all", "any") else out
     is_idx = op in ("argmax", "argmin")
     out = np.empty(max(n_out, 1), dtype=np.int64 if is_idx else np.float32)
     nd = -1 if dims is None else len(dims)
@@ -135,12 +155,22 @@ def reduce(op: str, x: np.ndarray, dims=None, keepdim: bool = False, correction:
     return out[:n_out].reshape(oshape)
 
 
-def ref_reduce(op: str, x: np.ndarray, dims=None, keepdim: bool = False, correction: int = 1):
+def ref_reduce(op: str, x: np.ndarray, dims=None, keepdim: bool = False, correction: int = 1, p: float = 2.0):
     """The reference's own compiled CPU code (requires oracle/_ref/libtpref.so)."""
     dims = _norm_dims(dims, x.ndim)
     sizes, strides = _prep(x)
     oshape = out_shape(x.shape, dims, keepdim)
     n_out = int(np.prod(oshape, dtype=np.int64)) if len(oshape) else 1
+    if op in _MORE:
+        out = np.empty(max(n_out, 1), dtype=np.uint8 if op in ("all", "any") else np.float32)
+        L = ref()
+        rc = L.tpref_reduce_more(OPS[op], x.ctypes.data, x.ndim, _arr(sizes), _arr(strides),
+                                 -1 if dims is None else len(dims), _arr(dims or []), int(keepdim), float(p),
+                                 out.ctypes.data, n_out)
+        if rc != 0:
+            raise RuntimeError(L.tpref_last_error().decode())
+        out = out[:n_out].reshape(oshape)
+        return out.astype(bool) if op in ("all", "any") else out
     is_idx = op in ("argmax", "argmin")
     out = np.empty(max(n_out, 1), dtype=np.int64 if is_idx else np.float32)
     nd = -1 if dims is None else len(dims)
@@ -179,11 +209,18 @@ def topk_sort(x, k, dim=-1, largest=True):
     return _topk(lib().tpo_topk_sort, x, k, dim, largest)
 
 
-def truth64(op: str, x: np.ndarray, dims=None, keepdim: bool = False, correction: int = 1):
+def truth64(op: str, x: np.ndarray, dims=None, keepdim: bool = False, correction: int = 1, p: float = 2.0):
     """float64 evaluation with numpy (pairwise summation in double): the accuracy anchor."""
     dims = _norm_dims(dims, x.ndim)
     ax = None if dims is None or len(dims) == 0 else tuple(d % x.ndim for d in dims)
     x64 = x.astype(np.float64)
+    if op == "prod":
+        return x64.prod(axis=ax, keepdims=keepdim)
+    if op == "norm":
+        a = np.abs(x64)
+        if np.isinf(p):
+            return a.max(axis=ax, keepdims=keepdim) if p > 0 else a.min(axis=ax, keepdims=keepdim)
+        return (a ** p).sum(axis=ax, keepdims=keepdim) ** (1.0 / p)
     if op == "sum":
         return x64.sum(axis=ax, keepdims=keepdim)
     if op == "mean":

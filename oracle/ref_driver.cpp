@@ -6,8 +6,9 @@
 // (p10/src/*.cpp, p10/src/backend/cpu/*Kernels.cpp and the file its generator emits); it
 // contains no reduction arithmetic of its own.  Every call goes through the reference's
 // generated Tensor methods and therefore through its Dispatcher:
-//   Tensor::sum/mean/max/min/argmax/argmin/var/std  ->  DispatchStub::call(name, CPU, ...)
-//   ->  tensorplay::cpu::*_kernel   (p10/src/backend/cpu/ReductionKernels.cpp:72-855)
+//   Tensor::sum/mean/max/min/argmax/argmin/var/std/prod/norm/all/any
+//   ->  DispatchStub::call(name, CPU, ...)
+//   ->  tensorplay::cpu::*_kernel   (p10/src/backend/cpu/ReductionKernels.cpp:72-872)
 #include "Tensor.h"
 
 #include <cstdint>
@@ -85,6 +86,44 @@ int tpref_reduce(int op, const float* in, int ndim, const int64_t* sizes, const 
         } else {
             if (rc.dtype() != DType::Float32) { g_err = "expected Float32 result"; return 4; }
             std::memcpy(out_val, rc.data_ptr<float>(), sizeof(float) * out_numel);
+        }
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return 1;
+    }
+}
+
+// op: 8 prod, 9 norm(p), 10 all, 11 any; dim conventions as tpref_reduce.  prod and norm write
+// floats to out, all and any one byte per output element.
+int tpref_reduce_more(int op, const float* in, int ndim, const int64_t* sizes, const int64_t* strides,
+                      int n_dims, const int64_t* dims, int keepdim, double p, void* out,
+                      int64_t out_numel) {
+    try {
+        Tensor x = wrap(in, ndim, sizes, strides);
+        std::vector<int64_t> d;
+        if (n_dims > 0) d.assign(dims, dims + n_dims);
+        const bool full = n_dims < 0;
+        const bool kd = keepdim != 0;
+        Tensor r;
+        switch (op) {
+            case 8: r = full ? x.prod(DType::Undefined) : x.prod(d, kd, DType::Undefined); break;
+            case 9: r = full ? x.norm(p) : x.norm(d, p, kd); break;
+            case 10: r = full ? x.all() : x.all(d, kd); break;
+            case 11: r = full ? x.any() : x.any(d, kd); break;
+            default: g_err = "unknown op"; return 2;
+        }
+        if (r.numel() != out_numel) {
+            g_err = "output element count mismatch: reference produced " + std::to_string(r.numel());
+            return 3;
+        }
+        Tensor rc = r.is_contiguous() ? r : r.clone();
+        if (op >= 10) {
+            if (rc.dtype() != DType::Bool) { g_err = "expected Bool result"; return 4; }
+            std::memcpy(out, rc.data_ptr<bool>(), sizeof(bool) * out_numel);
+        } else {
+            if (rc.dtype() != DType::Float32) { g_err = "expected Float32 result"; return 4; }
+            std::memcpy(out, rc.data_ptr<float>(), sizeof(float) * out_numel);
         }
         return 0;
     } catch (const std::exception& e) {

@@ -22,6 +22,15 @@
  *                    overload, float sequential for the dim overload); divide in DOUBLE by
  *                    max(0, n - corr); round to float (ReductionKernels.cpp:815-847)
  *   std              sqrtf(var) (ReductionKernels.cpp:849-855)
+ *   prod()           float accumulator from 1, multiplied element by element in row-major order
+ *                    (ReductionKernels.cpp:404-438); prod(dims): float output pre-filled with 1,
+ *                    out[o] *= in[i] over all input indices in row-major order (:441-513)
+ *   norm(p)          abs() in float; pow(p) evaluated in double and stored as float
+ *                    (pow_scalar_kernel, p10/src/backend/cpu/PointwiseKernels.cpp:392-396); the sum
+ *                    rule above; pow(1/p) the same way (ReductionKernels.cpp:858-872);
+ *                    p = +-inf: abs() then the max / min rule above
+ *   all/any          an element is true iff it is not zero, so NaN is true; all of nothing is
+ *                    true, any of nothing is false (ReductionKernels.cpp:517-563, 565-677)
  *
  * One deliberate difference: for argmax/argmin over a dim that is neither the last nor the
  * second-to-last of a >=3-D tensor the reference's CPU code writes its rows in a permuted order
@@ -46,7 +55,7 @@
 #define TPO_MAX_DIMS 16
 
 enum { TPO_SUM = 0, TPO_MEAN = 1, TPO_VAR = 2, TPO_STD = 3, TPO_MAX = 4, TPO_MIN = 5,
-       TPO_ARGMAX = 6, TPO_ARGMIN = 7 };
+       TPO_ARGMAX = 6, TPO_ARGMIN = 7, TPO_PROD = 8, TPO_NORM = 9, TPO_ALL = 10, TPO_ANY = 11 };
 
 typedef struct {
     int ndim;
@@ -234,6 +243,64 @@ int tpo_reduce(int op, const float* in, int ndim, const int64_t* sizes, const in
         free(best);
         return 0;
     }
+    default:
+        return -5;
+    }
+}
+
+
+/* prod, norm(p), all, any.  Same dim conventions as tpo_reduce.  prod and norm write floats to
+ * out; all and any write one byte (0/1) per output element to out.  Returns 0, -2 for a bad dim,
+ * -3 for norm(+-inf) of an empty tensor without a dim list. */
+int tpo_reduce_more(int op, const float* in, int ndim, const int64_t* sizes, const int64_t* strides,
+                    int n_dims, const int64_t* dims, double p, void* out) {
+    walk_t w;
+    int rc = setup(&w, ndim, sizes, strides, n_dims, dims);
+    if (rc) return rc;
+    const int full = n_dims <= 0;
+    float* of = (float*)out;
+    uint8_t* ob = (uint8_t*)out;
+    switch (op) {
+    case TPO_PROD:
+        if (full) {
+            float acc = 1.0f;
+            WALK_BEGIN(&w) acc *= in[ioff]; (void)ooff; WALK_END(&w)
+            of[0] = acc;
+        } else {
+            for (int64_t i = 0; i < w.out_numel; ++i) of[i] = 1.0f;
+            WALK_BEGIN(&w) of[ooff] *= in[ioff]; WALK_END(&w)
+        }
+        return 0;
+    case TPO_NORM:
+        if (isinf(p)) {
+            if (full && w.numel == 0) return -3;
+            const float init = p > 0 ? -INFINITY : INFINITY;
+            for (int64_t i = 0; i < w.out_numel; ++i) of[i] = init;
+            if (p > 0) {
+                WALK_BEGIN(&w) { float a = fabsf(in[ioff]); if (a > of[ooff]) of[ooff] = a; } WALK_END(&w)
+            } else {
+                WALK_BEGIN(&w) { float a = fabsf(in[ioff]); if (a < of[ooff]) of[ooff] = a; } WALK_END(&w)
+            }
+            return 0;
+        }
+        if (full) {
+            double acc = 0.0;
+            WALK_BEGIN(&w) { float t = (float)pow((double)fabsf(in[ioff]), p); acc += (double)t; (void)ooff; } WALK_END(&w)
+            of[0] = (float)pow((double)(float)acc, 1.0 / p);
+        } else {
+            for (int64_t i = 0; i < w.out_numel; ++i) of[i] = 0.0f;
+            WALK_BEGIN(&w) { float t = (float)pow((double)fabsf(in[ioff]), p); of[ooff] += t; } WALK_END(&w)
+            for (int64_t i = 0; i < w.out_numel; ++i) of[i] = (float)pow((double)of[i], 1.0 / p);
+        }
+        return 0;
+    case TPO_ALL:
+        for (int64_t i = 0; i < w.out_numel; ++i) ob[i] = 1;
+        WALK_BEGIN(&w) if (!(in[ioff] != 0.0f)) ob[ooff] = 0; WALK_END(&w)
+        return 0;
+    case TPO_ANY:
+        for (int64_t i = 0; i < w.out_numel; ++i) ob[i] = 0;
+        WALK_BEGIN(&w) if (in[ioff] != 0.0f) ob[ooff] = 1; WALK_END(&w)
+        return 0;
     default:
         return -5;
     }

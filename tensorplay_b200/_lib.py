@@ -15,7 +15,8 @@ LIB_PATH = os.path.join(_PKG, "libtpb200.so")
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_DIM_RANGE, ERR_EMPTY, ERR_WORKSPACE, ERR_CUDA = range(7)
 F32 = 0
 OP = {"sum": 0, "mean": 1, "var": 2, "std": 3, "max": 4, "min": 5, "argmax": 6, "argmin": 7,
-      "max_argmax": 8, "min_argmin": 9}
+      "max_argmax": 8, "min_argmin": 9, "prod": 10, "norm1": 11, "norm2": 12, "norm_inf": 13,
+      "norm_neg_inf": 14, "all": 15, "any": 16}
 PARTIAL_BYTES = 40
 MAX_DIMS = 8
 

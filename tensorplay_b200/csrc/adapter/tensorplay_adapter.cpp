@@ -12,6 +12,7 @@
 #include "Exception.h"
 
 #include <cstdint>
+#include <limits>
 #include <optional>
 #include <string>
 #include <vector>
@@ -30,6 +31,8 @@ struct Previous {
     void* max = nullptr; void* max_dim = nullptr; void* min = nullptr; void* min_dim = nullptr;
     void* argmax = nullptr; void* argmin = nullptr;
     void* var = nullptr; void* var_dim = nullptr; void* std_ = nullptr; void* std_dim = nullptr;
+    void* prod = nullptr; void* prod_dim = nullptr; void* norm = nullptr; void* norm_dim = nullptr;
+    void* all = nullptr; void* all_dim = nullptr; void* any = nullptr; void* any_dim = nullptr;
 } g_prev;
 
 void* lookup(const char* name) {
@@ -69,7 +72,8 @@ Tensor run(int op, const Tensor& self, uint64_t mask, int index_dim, int64_t cor
     const IntList sizes = static_cast<IntList>(self.shape());
     const IntList strides = self.strides();
     const bool idx = op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN;
-    Tensor out(out_shape, idx ? DType::Int64 : DType::Float32, self.device());
+    const bool boolean = op == TPB200_OP_ALL || op == TPB200_OP_ANY;
+    Tensor out(out_shape, idx ? DType::Int64 : (boolean ? DType::Bool : DType::Float32), self.device());
     const size_t ws_bytes = tpb200_reduce_workspace_bytes(op, TPB200_F32, nd, sizes.data(), strides.data(), mask);
     Tensor ws;
     if (ws_bytes) ws = Tensor(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
@@ -89,7 +93,7 @@ Tensor fallthrough(void* prev, const char* name, A&&... a) {
     return reinterpret_cast<Fn>(prev)(std::forward<A>(a)...);
 }
 
-// ---- the fourteen kernels ---------------------------------------------------------------------
+// ---- the kernels ------------------------------------------------------------------------------
 Tensor tpb_sum(const Tensor& self, DType dtype) {
     if (!ours(self) || !same_dtype(dtype)) return fallthrough<Tensor (*)(const Tensor&, DType)>(g_prev.sum, "sum", self, dtype);
     return run(TPB200_OP_SUM, self, 0, -1, 1, {});
@@ -162,6 +166,56 @@ Tensor tpb_std_dim(const Tensor& self, const IntList& dim, int64_t correction, b
     return run(TPB200_OP_STD, self, m, -1, correction, shape);
 }
 
+Tensor tpb_prod(const Tensor& self, DType dtype) {
+    if (!ours(self) || !same_dtype(dtype)) return fallthrough<Tensor (*)(const Tensor&, DType)>(g_prev.prod, "prod", self, dtype);
+    return run(TPB200_OP_PROD, self, 0, -1, 1, {});
+}
+Tensor tpb_prod_dim(const Tensor& self, const IntList& dim, bool keepdim, DType dtype) {
+    if (!ours(self) || !same_dtype(dtype))
+        return fallthrough<Tensor (*)(const Tensor&, const IntList&, bool, DType)>(g_prev.prod_dim, "prod", self, dim, keepdim, dtype);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_PROD, self, m, -1, 1, shape);
+}
+// p = 1, 2, +-inf run here; any other p goes to the kernel registered before (the reference's own
+// CUDA kernel rejects everything but p = 2: ReductionKernels.cu:296-321)
+int norm_op(double p) {
+    if (p == 1.0) return TPB200_OP_NORM1;
+    if (p == 2.0) return TPB200_OP_NORM2;
+    if (p == std::numeric_limits<double>::infinity()) return TPB200_OP_NORM_INF;
+    if (p == -std::numeric_limits<double>::infinity()) return TPB200_OP_NORM_NEG_INF;
+    return -1;
+}
+Tensor tpb_norm(const Tensor& self, double p) {
+    const int op = norm_op(p);
+    if (!ours(self) || op < 0) return fallthrough<Tensor (*)(const Tensor&, double)>(g_prev.norm, "norm", self, p);
+    return run(op, self, 0, -1, 1, {});
+}
+Tensor tpb_norm_dim(const Tensor& self, const IntList& dim, double p, bool keepdim) {
+    const int op = norm_op(p);
+    if (!ours(self) || op < 0)
+        return fallthrough<Tensor (*)(const Tensor&, const IntList&, double, bool)>(g_prev.norm_dim, "norm", self, dim, p, keepdim);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(op, self, m, -1, 1, shape);
+}
+Tensor tpb_all(const Tensor& self) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&)>(g_prev.all, "all", self);
+    return run(TPB200_OP_ALL, self, 0, -1, 1, {});
+}
+Tensor tpb_all_dim(const Tensor& self, const IntList& dim, bool keepdim) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, const IntList&, bool)>(g_prev.all_dim, "all", self, dim, keepdim);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_ALL, self, m, -1, 1, shape);
+}
+Tensor tpb_any(const Tensor& self) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&)>(g_prev.any, "any", self);
+    return run(TPB200_OP_ANY, self, 0, -1, 1, {});
+}
+Tensor tpb_any_dim(const Tensor& self, const IntList& dim, bool keepdim) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&, const IntList&, bool)>(g_prev.any_dim, "any", self, dim, keepdim);
+    IntList shape; const uint64_t m = mask_and_shape(self, dim, keepdim, &shape);
+    return run(TPB200_OP_ANY, self, m, -1, 1, shape);
+}
+
 }  // namespace
 
 namespace tensorplay {
@@ -174,6 +228,10 @@ TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
     g_prev.argmax = lookup("argmax");   g_prev.argmin = lookup("argmin");
     g_prev.var = lookup("var");         g_prev.var_dim = lookup("var.dim");
     g_prev.std_ = lookup("std");        g_prev.std_dim = lookup("std.dim");
+    g_prev.prod = lookup("prod");       g_prev.prod_dim = lookup("prod.dim_IntList");
+    g_prev.norm = lookup("norm");       g_prev.norm_dim = lookup("norm.dim");
+    g_prev.all = lookup("all");         g_prev.all_dim = lookup("all.dim");
+    g_prev.any = lookup("any");         g_prev.any_dim = lookup("any.dim");
     m.impl("sum", tpb_sum);             m.impl("sum.dim_IntList", tpb_sum_dim);
     m.impl("mean", tpb_mean);           m.impl("mean.dim", tpb_mean_dim);
     m.impl("max", tpb_max);             m.impl("max.dim", tpb_max_dim);
@@ -181,6 +239,10 @@ TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
     m.impl("argmax", tpb_argmax);       m.impl("argmin", tpb_argmin);
     m.impl("var", tpb_var);             m.impl("var.dim", tpb_var_dim);
     m.impl("std", tpb_std);             m.impl("std.dim", tpb_std_dim);
+    m.impl("prod", tpb_prod);           m.impl("prod.dim_IntList", tpb_prod_dim);
+    m.impl("norm", tpb_norm);           m.impl("norm.dim", tpb_norm_dim);
+    m.impl("all", tpb_all);             m.impl("all.dim", tpb_all_dim);
+    m.impl("any", tpb_any);             m.impl("any.dim", tpb_any_dim);
 }
 
 }  // namespace tensorplay

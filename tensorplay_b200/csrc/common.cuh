@@ -184,12 +184,15 @@ struct MomAcc {
 // (every comparison with NaN is false), -0.0 and +0.0 tie.  Positions grow along a thread's
 // own scan, so the strict compare keeps the thread's first occurrence; between threads a tie
 // goes to the lower position.
-template <bool IS_MAX>
+// ABS: the extremum of |x| (norm with p = +-inf: the reference computes abs().max() / abs().min(),
+// p10/src/backend/cpu/ReductionKernels.cpp:858-872, with the same scan rule).
+template <bool IS_MAX, bool ABS = false>
 struct ExtAcc {
     float v;
     long long i;
     __device__ __forceinline__ void init() { v = IS_MAX ? -INFINITY : INFINITY; i = kNoIndex; }
     __device__ __forceinline__ void add(float x, long long pos) {
+        if (ABS) x = fabsf(x);
         bool better = IS_MAX ? (x > v) : (x < v);
         if (better) { v = x; i = pos; }
     }
@@ -209,6 +212,69 @@ struct ExtAcc {
     }
     __device__ __forceinline__ void store(Packed* p) const { p->d0 = 0; p->d1 = 0; p->d2 = 0; p->i0 = i; p->f0 = v; p->pad = 0; }
     __device__ __forceinline__ void load(const Packed* p) { v = p->f0; i = p->i0; }
+};
+
+// Sum of |x| (F = 0) or of x*x (F = 1) in fp64: the norms with p = 1 and p = 2.  The reference
+// forms abs().pow(p).sum().pow(1/p) in float32 (ReductionKernels.cpp:858-872); here every term and
+// the sum are exact to fp64 rounding and the result is rounded once.
+template <int F>
+struct PowSumAcc {
+    double s;
+    __device__ __forceinline__ void init() { s = 0.0; }
+    __device__ __forceinline__ void add(float x, long long) {
+        const double d = (double)x;
+        if (F == 0) s += fabs(d); else s = fma(d, d, s);
+    }
+    __device__ __forceinline__ void add4(float x0, float x1, float x2, float x3, long long, long long) {
+        add(x0, 0); add(x1, 0); add(x2, 0); add(x3, 0);
+    }
+    __device__ __forceinline__ void finish_thread() {}
+    __device__ __forceinline__ void merge(const PowSumAcc& o) { s += o.s; }
+    __device__ __forceinline__ PowSumAcc shfl_down(int d) const {
+        PowSumAcc r; r.s = __shfl_down_sync(kFull, s, d); return r;
+    }
+    __device__ __forceinline__ void store(Packed* p) const { p->d0 = s; p->d1 = 0; p->d2 = 0; p->i0 = 0; p->f0 = 0; p->pad = 0; }
+    __device__ __forceinline__ void load(const Packed* p) { s = p->d0; }
+};
+
+// Product in fp64 (the reference multiplies float32 values one after the other,
+// ReductionKernels.cpp:404-438, 441-513); an empty product is 1.
+struct ProdAcc {
+    double p;
+    __device__ __forceinline__ void init() { p = 1.0; }
+    __device__ __forceinline__ void add(float x, long long) { p *= (double)x; }
+    __device__ __forceinline__ void add4(float x0, float x1, float x2, float x3, long long, long long) {
+        p *= ((double)x0 * (double)x1) * ((double)x2 * (double)x3);
+    }
+    __device__ __forceinline__ void finish_thread() {}
+    __device__ __forceinline__ void merge(const ProdAcc& o) { p *= o.p; }
+    __device__ __forceinline__ ProdAcc shfl_down(int d) const {
+        ProdAcc r; r.p = __shfl_down_sync(kFull, p, d); return r;
+    }
+    __device__ __forceinline__ void store(Packed* q) const { q->d0 = p; q->d1 = 0; q->d2 = 0; q->i0 = 0; q->f0 = 0; q->pad = 0; }
+    __device__ __forceinline__ void load(const Packed* q) { p = q->d0; }
+};
+
+// all / any: an element counts as true iff it is not zero (static_cast<bool>, so NaN is true:
+// ReductionKernels.cpp:517-563, 565-677); all of nothing is true, any of nothing is false.
+template <bool IS_ALL>
+struct BoolAcc {
+    unsigned f;
+    __device__ __forceinline__ void init() { f = IS_ALL ? 1u : 0u; }
+    __device__ __forceinline__ void add(float x, long long) {
+        const unsigned nz = x != 0.0f ? 1u : 0u;
+        f = IS_ALL ? (f & nz) : (f | nz);
+    }
+    __device__ __forceinline__ void add4(float x0, float x1, float x2, float x3, long long, long long) {
+        add(x0, 0); add(x1, 0); add(x2, 0); add(x3, 0);
+    }
+    __device__ __forceinline__ void finish_thread() {}
+    __device__ __forceinline__ void merge(const BoolAcc& o) { f = IS_ALL ? (f & o.f) : (f | o.f); }
+    __device__ __forceinline__ BoolAcc shfl_down(int d) const {
+        BoolAcc r; r.f = __shfl_down_sync(kFull, f, d); return r;
+    }
+    __device__ __forceinline__ void store(Packed* p) const { p->d0 = 0; p->d1 = 0; p->d2 = 0; p->i0 = (long long)f; p->f0 = 0; p->pad = 0; }
+    __device__ __forceinline__ void load(const Packed* p) { f = (unsigned)p->i0; }
 };
 
 // Fixed-order tree over the 32 lanes; lane 0 holds the result.
@@ -255,8 +321,19 @@ __device__ __forceinline__ void write_result(const MomAcc& a, const Epilogue& e,
     float var = count == 0.0 ? NAN : (float)(a.m2 / dv);
     ov[o] = e.op == TPB200_OP_STD ? sqrtf(var) : var;
 }
-template <bool IS_MAX>
-__device__ __forceinline__ void write_result(const ExtAcc<IS_MAX>& a, const Epilogue& e, double, float* ov, long long* oi, long long o) {
+template <int F>
+__device__ __forceinline__ void write_result(const PowSumAcc<F>& a, const Epilogue&, double, float* ov, long long*, long long o) {
+    ov[o] = F == 0 ? (float)a.s : (float)sqrt(a.s);
+}
+__device__ __forceinline__ void write_result(const ProdAcc& a, const Epilogue&, double, float* ov, long long*, long long o) {
+    ov[o] = (float)a.p;
+}
+template <bool IS_ALL>
+__device__ __forceinline__ void write_result(const BoolAcc<IS_ALL>& a, const Epilogue&, double, float* ov, long long*, long long o) {
+    reinterpret_cast<unsigned char*>(ov)[o] = (unsigned char)a.f;   // Bool output: one byte per element
+}
+template <bool IS_MAX, bool ABS>
+__device__ __forceinline__ void write_result(const ExtAcc<IS_MAX, ABS>& a, const Epilogue& e, double, float* ov, long long* oi, long long o) {
     // nothing compared better (empty, all NaN, or all equal to the start value): index 0 and the
     // start value, as in the reference's scan (ReductionKernels.cpp:692-694, 727-735)
     if (ov) ov[o] = a.v;

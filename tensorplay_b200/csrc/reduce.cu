@@ -320,7 +320,9 @@ generic_kernel(const float* __restrict__ in, GenGeom g, Epilogue e, float* ov, l
 }
 
 // ------------------------------------------------------------------ planner ----------------
-enum Family { FAM_SUM, FAM_MOM, FAM_MAX, FAM_MIN };
+enum Family { FAM_SUM, FAM_MOM, FAM_MAX, FAM_MIN,
+              // whole-op families without a sharded form
+              FAM_PROD, FAM_NORM1, FAM_NORM2, FAM_ABSMAX, FAM_ABSMIN, FAM_ALL, FAM_ANY };
 enum Strategy { ST_NONE, ST_ROW_WARP, ST_ROW_CTA, ST_ROW_SPLIT, ST_COL, ST_GENERIC };
 
 struct Plan {
@@ -344,6 +346,13 @@ static int family_of(int op, Family* f) {
         case TPB200_OP_VAR: case TPB200_OP_STD: *f = FAM_MOM; return 0;
         case TPB200_OP_MAX: case TPB200_OP_ARGMAX: case TPB200_OP_MAX_ARGMAX: *f = FAM_MAX; return 0;
         case TPB200_OP_MIN: case TPB200_OP_ARGMIN: case TPB200_OP_MIN_ARGMIN: *f = FAM_MIN; return 0;
+        case TPB200_OP_PROD: *f = FAM_PROD; return 0;
+        case TPB200_OP_NORM1: *f = FAM_NORM1; return 0;
+        case TPB200_OP_NORM2: *f = FAM_NORM2; return 0;
+        case TPB200_OP_NORM_INF: *f = FAM_ABSMAX; return 0;
+        case TPB200_OP_NORM_NEG_INF: *f = FAM_ABSMIN; return 0;
+        case TPB200_OP_ALL: *f = FAM_ALL; return 0;
+        case TPB200_OP_ANY: *f = FAM_ANY; return 0;
         default: return 1;
     }
 }
@@ -590,10 +599,10 @@ extern "C" int tpb200_reduce(int op, const void* in, int dtype, int ndim, const 
         }
     }
     if (pl.outs == 0) return TPB200_OK;
-    if (wants_val && (fam == FAM_MAX || fam == FAM_MIN) && pl.count == 0 && reduce_mask == 0) {
+    if (wants_val && (fam == FAM_MAX || fam == FAM_MIN || fam == FAM_ABSMAX || fam == FAM_ABSMIN) && pl.count == 0 && reduce_mask == 0) {
         // the overload without a dim argument on an empty tensor (ReductionKernels.cpp:240, :326);
         // with an explicit dim list the reference fills the output with the start value instead
-        return fail(TPB200_ERR_EMPTY, "%s(): Expected reduction dim to be non-empty", fam == FAM_MAX ? "max" : "min");
+        return fail(TPB200_ERR_EMPTY, "%s(): Expected reduction dim to be non-empty", (fam == FAM_MAX || fam == FAM_ABSMAX) ? "max" : "min");
     }
     if (!in && pl.count > 0) return fail(TPB200_ERR_INVALID, "input pointer is NULL");
     if (wants_val && !out_val) return fail(TPB200_ERR_INVALID, "out_val is NULL");
@@ -611,6 +620,13 @@ extern "C" int tpb200_reduce(int op, const void* in, int dtype, int ndim, const 
         case FAM_MOM: return launch_plan<MomAcc>(pl, x, e, ov, oi, workspace, st);
         case FAM_MAX: return launch_plan<ExtAcc<true>>(pl, x, e, ov, oi, workspace, st);
         case FAM_MIN: return launch_plan<ExtAcc<false>>(pl, x, e, ov, oi, workspace, st);
+        case FAM_PROD: return launch_plan<ProdAcc>(pl, x, e, ov, oi, workspace, st);
+        case FAM_NORM1: return launch_plan<PowSumAcc<0>>(pl, x, e, ov, oi, workspace, st);
+        case FAM_NORM2: return launch_plan<PowSumAcc<1>>(pl, x, e, ov, oi, workspace, st);
+        case FAM_ABSMAX: return launch_plan<ExtAcc<true, true>>(pl, x, e, ov, oi, workspace, st);
+        case FAM_ABSMIN: return launch_plan<ExtAcc<false, true>>(pl, x, e, ov, oi, workspace, st);
+        case FAM_ALL: return launch_plan<BoolAcc<true>>(pl, x, e, ov, oi, workspace, st);
+        case FAM_ANY: return launch_plan<BoolAcc<false>>(pl, x, e, ov, oi, workspace, st);
     }
     return fail(TPB200_ERR_INVALID, "internal: bad family");
 }
@@ -668,6 +684,7 @@ extern "C" int tpb200_reduce_partial(int family, const void* in, int dtype, int6
                                      size_t workspace_bytes, void* stream) {
     Family fam;
     if (family_of(family, &fam)) return fail(TPB200_ERR_INVALID, "unknown reduction family %d", family);
+    if (fam > FAM_MIN) return fail(TPB200_ERR_UNSUPPORTED, "operator %d has no sharded form", family);
     if (dtype != TPB200_F32) return fail(TPB200_ERR_UNSUPPORTED, "only float32 input is supported (dtype code %d)", dtype);
     if (n < 0) return fail(TPB200_ERR_INVALID, "negative element count");
     if (!partial_out) return fail(TPB200_ERR_INVALID, "partial_out is NULL");
@@ -693,6 +710,7 @@ extern "C" int tpb200_reduce_combine(int op, const void* partials, int n_parts, 
                                      int64_t correction, void* out_val, int64_t* out_idx, void* stream) {
     Family fam;
     if (family_of(op, &fam)) return fail(TPB200_ERR_INVALID, "unknown reduction operator %d", op);
+    if (fam > FAM_MIN) return fail(TPB200_ERR_UNSUPPORTED, "operator %d has no sharded form", op);
     if (n_parts < 1 || !partials) return fail(TPB200_ERR_INVALID, "need at least one partial record");
     const bool wants_val = !(op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN);
     const bool wants_idx = op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN || op == TPB200_OP_MAX_ARGMAX || op == TPB200_OP_MIN_ARGMIN;
@@ -752,6 +770,7 @@ extern "C" int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int6
                                          void* out_val, int64_t* out_idx, void* stream) {
     Family fam;
     if (family_of(op, &fam)) return fail(TPB200_ERR_INVALID, "unknown reduction operator %d", op);
+    if (fam > FAM_MIN) return fail(TPB200_ERR_UNSUPPORTED, "operator %d has no sharded form", op);
     if (dtype != TPB200_F32) return fail(TPB200_ERR_UNSUPPORTED, "only float32 input is supported (dtype code %d)", dtype);
     if (n < 0) return fail(TPB200_ERR_INVALID, "negative element count");
     if ((uint64_t)n > (uint64_t)TPB200_NOALLOC_MAX_ELEMENTS)
@@ -894,6 +913,7 @@ extern "C" int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, i
                                             void* workspace, size_t workspace_bytes, void* stream) {
     Family fam;
     if (family_of(op, &fam)) return fail(TPB200_ERR_INVALID, "unknown reduction operator %d", op);
+    if (fam > FAM_MIN) return fail(TPB200_ERR_UNSUPPORTED, "operator %d has no sharded form", op);
     if (dtype != TPB200_F32) return fail(TPB200_ERR_UNSUPPORTED, "only float32 input is supported (dtype code %d)", dtype);
     if (n < 0 || total_count < n) return fail(TPB200_ERR_INVALID, "bad element counts");
     if (world < 1 || world > kMaxPeers) return fail(TPB200_ERR_UNSUPPORTED, "1..%d ranks are supported, %d given", kMaxPeers, world);

@@ -8,6 +8,9 @@ Names, argument meaning and error behaviour follow the reference's Tensor method
     max(x, dim=None, keepdim=False)  -> values only, as max.dim in the reference
     min(...)                            (native_functions.yaml:720-733)
     argmax(x, dim=None, keepdim=False)                  argmin(...) likewise
+    prod(x, dim=None, keepdim=False, *, dtype=None)
+    norm(x, p=2.0, dim=None, keepdim=False)             p in {1, 2, inf, -inf}
+    all(x, dim=None, keepdim=False) / any(...)          -> bool tensor
     topk(x, k, dim=-1, largest=True, sorted=True) -> (values, indices)   [new operator]
     max_with_indices / min_with_indices(x, dim, keepdim=False) -> (values, indices), one pass
 
@@ -96,17 +99,18 @@ def _reduce(op: str, x: torch.Tensor, dim, keepdim: bool, correction: int = 1, i
     shape = _out_shape(x, dims, keepdim)
     want_val = op not in ("argmax", "argmin")
     want_idx = op in ("argmax", "argmin", "max_argmax", "min_argmin")
+    val_dtype = torch.bool if op in ("all", "any") else torch.float32
     with torch.cuda.device(x.device):
         if out is not None:
             outs = list(out) if isinstance(out, (tuple, list)) else [out]
             ov = outs.pop(0) if want_val else None
             oi = outs.pop(0) if want_idx else None
             if ov is not None:
-                _check_out(ov, shape, torch.float32, x.device, op)
+                _check_out(ov, shape, val_dtype, x.device, op)
             if oi is not None:
                 _check_out(oi, shape, torch.int64, x.device, op)
         else:
-            ov = torch.empty(shape, dtype=torch.float32, device=x.device) if want_val else None
+            ov = torch.empty(shape, dtype=val_dtype, device=x.device) if want_val else None
             oi = torch.empty(shape, dtype=torch.int64, device=x.device) if want_idx else None
         nbytes = L.tpb200_reduce_workspace_bytes(_lib.OP[op], _lib.F32, nd, sizes, strides, mask)
         ws = _workspace(x.device, nbytes)
@@ -150,6 +154,34 @@ def max(x, dim=None, keepdim=False, *, out=None):
 
 def min(x, dim=None, keepdim=False, *, out=None):
     return _reduce("min", x, dim, keepdim, out=out)
+
+
+def prod(x, dim=None, keepdim=False, *, dtype=None, out=None):
+    """prod / prod.dim_IntList (config/native_functions.yaml:735-743)."""
+    _check_dtype(dtype, "prod")
+    return _reduce("prod", x, dim, keepdim, out=out)
+
+
+def norm(x, p=2.0, dim=None, keepdim=False, *, out=None):
+    """norm / norm.dim (config/native_functions.yaml:801-809).  The reference's CUDA path has
+    p = 2 only (p10/src/backend/cuda/ReductionKernels.cu:296-321); its CPU path takes any p
+    (p10/src/backend/cpu/ReductionKernels.cpp:858-872).  Here: p = 1, 2, inf, -inf."""
+    p = float(p)
+    op = {1.0: "norm1", 2.0: "norm2", float("inf"): "norm_inf", float("-inf"): "norm_neg_inf"}.get(p)
+    if op is None:
+        raise NotImplementedError("norm: only p = 1, 2, inf and -inf are supported")
+    return _reduce(op, x, dim, keepdim, out=out)
+
+
+def all(x, dim=None, keepdim=False, *, out=None):
+    """all / all.dim (config/native_functions.yaml:756-764): bool result, true iff every element
+    is non-zero."""
+    return _reduce("all", x, dim, keepdim, out=out)
+
+
+def any(x, dim=None, keepdim=False, *, out=None):
+    """any / any.dim (config/native_functions.yaml:766-774)."""
+    return _reduce("any", x, dim, keepdim, out=out)
 
 
 def _arg(op, x, dim, keepdim, out=None):

@@ -10,6 +10,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <limits>
 #include <vector>
 
 using namespace tensorplay;
@@ -46,6 +47,15 @@ static void equal_i(const char* what, const Tensor& gpu, const Tensor& cpu) {
     for (size_t i = 0; i < g.size(); ++i)
         if (g[i] != c[i]) { printf("FAIL %s: [%zu] gpu %lld cpu %lld\n", what, i, (long long)g[i], (long long)c[i]); ++fails; return; }
 }
+static void equal_bool(const char* what, const Tensor& gpu, const Tensor& cpu) {
+    ++checks;
+    if (gpu.dtype() != DType::Bool) { printf("FAIL %s: not a Bool tensor\n", what); ++fails; return; }
+    auto g = to_host<unsigned char>(gpu);
+    const bool* c = cpu.data_ptr<bool>();
+    if ((int64_t)g.size() != cpu.numel()) { printf("FAIL %s: shape\n", what); ++fails; return; }
+    for (size_t i = 0; i < g.size(); ++i)
+        if ((g[i] != 0) != c[i]) { printf("FAIL %s: [%zu] gpu %d cpu %d\n", what, i, (int)g[i], (int)c[i]); ++fails; return; }
+}
 static void equal_bits(const char* what, const Tensor& gpu, const Tensor& cpu) {
     ++checks;
     auto g = to_host<float>(gpu);
@@ -81,6 +91,23 @@ int main() {
     Tensor ct(c.impl()->storage(), {C, R}, {1, C}, DType::Float32, 0);
     close_f("sum(dim=0) of a transposed view", gt.sum({0}, false, DType::Undefined), ct.sum({0}, false, DType::Undefined), 1e-5, tol);
     equal_i("argmax(1) of a transposed view", gt.argmax(std::optional<int64_t>(1), false), ct.argmax(std::optional<int64_t>(1), false));
+    // the other operators of the registration block: prod, norm, all, any
+    std::vector<float> w(R * C);
+    for (size_t i = 0; i < w.size(); ++i) { s = s * 1664525u + 1013904223u; w[i] = 0.9f + (float)((s >> 8) % 201) / 1000.0f; }
+    w[5 * C + 17] = 0.0f;
+    Tensor cw = Tensor::tensor<float>(w).reshape({R, C});
+    Tensor gw = to_cuda(cw);
+    close_f("prod(dim=1)", gw.prod({1}, false, DType::Undefined), cw.prod({1}, false, DType::Undefined), 1e-4, 0);
+    close_f("prod()", gw.prod(DType::Undefined), cw.prod(DType::Undefined), 1e-4, 0);
+    close_f("norm()", g.norm(2.0), c.norm(2.0), 1e-5, 0);
+    close_f("norm(dim=0,p=2,keepdim)", g.norm({0}, 2.0, true), c.norm({0}, 2.0, true), 1e-5, 0);
+    close_f("norm(dim=1,p=1)", g.norm({1}, 1.0, false), c.norm({1}, 1.0, false), 1e-5, 0);
+    equal_bits("norm(dim=1,p=inf)", g.norm({1}, std::numeric_limits<double>::infinity(), false),
+               c.norm({1}, std::numeric_limits<double>::infinity(), false));
+    equal_bool("all(dim=1)", gw.all({1}, false), cw.all({1}, false));
+    equal_bool("any(dim=0,keepdim)", gw.any({0}, true), cw.any({0}, true));
+    equal_bool("all()", gw.all(), cw.all());
+    equal_bool("any()", gw.any(), cw.any());
     // errors keep the reference's type and message
     try { g.sum({2}, false, DType::Undefined); printf("FAIL: no error for a bad dim\n"); ++fails; }
     catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "Dimension out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import oracle as O  # noqa: E402
 
-OPS = ["sum", "mean", "var", "std", "max", "min", "argmax", "argmin"]
+OPS = ["sum", "mean", "var", "std", "max", "min", "argmax", "argmin", "prod", "norm", "all", "any"]
 
 
 def cases():
@@ -56,12 +56,13 @@ def main():
                 # second-to-last dim of a >= 3-D tensor (p10/src/backend/cpu/ReductionKernels.cpp:714-735)
                 if dims is not None and x.ndim >= 3 and dims[0] % x.ndim not in (x.ndim - 1, x.ndim - 2):
                     continue
-            if op in ("sum", "mean", "var", "std") and not np.all(np.isfinite(x)):
+            if op in ("sum", "mean", "var", "std", "prod", "norm") and not np.all(np.isfinite(x)):
                 continue
             for corr in ((0, 1) if op in ("var", "std") else (1,)):
-                key = f"r{len(index)}"
-                arrays[key] = O.ref_reduce(op, x, dims, False, corr)
-                index.append({"x": xi, "op": op, "dims": dims, "correction": corr, "out": key})
+                for p in ((1.0, 2.0, "inf", "-inf") if op == "norm" else (2.0,)):
+                    key = f"r{len(index)}"
+                    arrays[key] = O.ref_reduce(op, x, dims, False, corr, float(p))
+                    index.append({"x": xi, "op": op, "dims": dims, "correction": corr, "p": float(p), "out": key})
         n += 1
     arrays["index_json"] = np.frombuffer(json.dumps(index).encode(), dtype=np.uint8)
     out = os.path.join(HERE, "reduce_golden.npz")

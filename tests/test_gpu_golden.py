@@ -31,6 +31,17 @@ def test_gpu_matches_reference_golden(cuda):
             assert_index_equal(got, want, what)
         elif op in ("max", "min"):
             assert_bits_equal(getattr(tpb, op)(xg, dims).cpu().numpy(), want, what)
+        elif op in ("all", "any"):
+            got = getattr(tpb, op)(xg, dims).cpu().numpy()
+            assert got.dtype == np.bool_ and np.array_equal(got, want.astype(bool)), what
+        elif op == "norm" and np.isinf(e["p"]):
+            assert_bits_equal(tpb.norm(xg, e["p"], dims).cpu().numpy(), want, what)     # an extremum of |x|: exact
+        elif op in ("prod", "norm"):
+            got = (tpb.prod(xg, dims) if op == "prod" else tpb.norm(xg, e["p"], dims)).cpu().numpy()
+            truth = O.truth64(op, x, dims, False, corr, e["p"])
+            assert_close64(got, truth, what)
+            # the reference multiplies / adds in float32 one element after the other
+            assert_close64(got, want.astype(np.float64), what + " vs reference", rel=1e-4)
         else:
             got = (getattr(tpb, op)(xg, dims, corr) if op in ("var", "std") else getattr(tpb, op)(xg, dims)).cpu().numpy()
             truth = O.truth64(op, x, dims, False, corr)

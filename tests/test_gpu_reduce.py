@@ -268,3 +268,60 @@ def test_run_to_run_bit_identity(cuda):
         a = fn(x, *args).clone()
         for _ in range(3):
             assert torch.equal(a.view(torch.int32), fn(x, *args).view(torch.int32))
+
+
+def _more_cases():
+    rng = np.random.default_rng(41)
+    x = (rng.standard_normal((37, 1000)) * 0.2 + 1.0).astype(np.float32)      # products stay in range
+    y = rng.uniform(-1, 1, (6, 130, 24)).astype(np.float32)
+    z = rng.integers(0, 2, (33, 70, 9)).astype(np.float32)
+    z[:, ::7, :] = 1.0
+    z[3, 5, 2] = np.nan
+    return x, y, z
+
+
+def test_prod_norm_all_any_against_oracle_and_float64(cuda):
+    """The other operators of the reference's registration block
+    (p10/src/backend/cuda/ReductionKernels.cu:256-267, 296-345): prod and norm within 1e-5 of float64
+    (and 1e-4 of the reference's float32 chain), norm(+-inf) and all/any exact."""
+    import torch
+    import tensorplay_b200 as tpb
+    from oracle import oracle as O
+
+    x, y, z = _more_cases()
+    for a, dimss in ((x, [None, [1], [0], [-1]]), (y, [None, [0], [1], [2], [0, 2], [1, 2]]),
+                     (y.transpose(2, 0, 1), [None, [0], [2], [0, 1]]), (y[:, ::3, 1:23], [[1], [2], None])):
+        ag = gpu_view(a, cuda)
+        for dims in dimss:
+            for kd in (False, True):
+                what = f"shape={a.shape} dims={dims} keepdim={kd}"
+                got = tpb.prod(ag, dims, kd).cpu().numpy()
+                assert_close64(got, O.truth64("prod", a, dims, kd), "prod " + what)
+                assert_close64(got, O.reduce("prod", a, dims, kd).astype(np.float64), "prod vs oracle " + what, rel=1e-4)
+                for p in (1.0, 2.0):
+                    got = tpb.norm(ag, p, dims, kd).cpu().numpy()
+                    assert_close64(got, O.truth64("norm", a, dims, kd, p=p), f"norm p={p} " + what)
+                    assert_close64(got, O.reduce("norm", a, dims, kd, p=p).astype(np.float64), f"norm p={p} vs oracle " + what, rel=1e-4)
+                for p in (float("inf"), float("-inf")):
+                    assert_bits_equal(tpb.norm(ag, p, dims, kd).cpu().numpy(), O.reduce("norm", a, dims, kd, p=p), f"norm p={p} " + what)
+    zg = torch.from_numpy(z).to(cuda)
+    for dims in (None, [0], [1], [2], [0, 2], [1, 2]):
+        for op in ("all", "any"):
+            got = getattr(tpb, op)(zg, dims).cpu().numpy()
+            assert got.dtype == np.bool_ and np.array_equal(got, O.reduce(op, z, dims)), (op, dims)
+    zeros = torch.zeros(5, 3000, device=cuda)
+    assert not bool(tpb.any(zeros)) and not bool(tpb.all(zeros))
+    zeros[2, 2999] = float("nan")                                   # NaN counts as true
+    assert bool(tpb.any(zeros)) and tpb.any(zeros, 1).cpu().tolist() == [False, False, True, False, False]
+    ones = torch.ones(1 << 22, device=cuda)
+    assert bool(tpb.all(ones))
+    ones[4_000_001] = 0.0
+    assert not bool(tpb.all(ones)) and float(tpb.prod(ones)) == 0.0
+    # empty reductions: prod of nothing is 1, norm 0, all true, any false
+    e = torch.empty(4, 0, device=cuda)
+    assert tpb.prod(e, 1).cpu().tolist() == [1.0] * 4 and tpb.norm(e, 2.0, 1).cpu().tolist() == [0.0] * 4
+    assert tpb.all(e, 1).cpu().tolist() == [True] * 4 and tpb.any(e, 1).cpu().tolist() == [False] * 4
+    with pytest.raises(NotImplementedError):
+        tpb.norm(ones, 3.0)
+    with pytest.raises(RuntimeError, match="non-empty"):
+        tpb.norm(torch.empty(0, device=cuda), float("inf"))

@@ -40,6 +40,15 @@ def test_known_answers_of_the_reference_tests():
     assert abs(float(O.reduce("std", z)) - (5.0 / 3.0) ** 0.5) < 1e-6
     w = np.array([1.0, 5.0, 2.0, 8.0], dtype=np.float32)
     assert O.reduce("argmax", w) == 3 and O.reduce("argmin", w) == 0
+    # test/test_reduction.py:5-33 (prod, all/any), test/test_cuda_reductions.py:66-75 (prod, norm)
+    assert O.reduce("prod", y) == 24.0
+    assert O.reduce("prod", y, [0]).tolist() == [3.0, 8.0] and O.reduce("prod", y, [1]).tolist() == [2.0, 12.0]
+    b = np.array([[1, 0], [1, 1]], dtype=np.float32)
+    assert bool(O.reduce("any", b)) and not bool(O.reduce("all", b))
+    assert bool(O.reduce("all", np.array([1, 1], dtype=np.float32)))
+    assert not bool(O.reduce("any", np.array([0, 0], dtype=np.float32)))
+    assert O.reduce("all", b, [0]).tolist() == [True, False]
+    assert O.reduce("norm", np.array([3.0, 4.0], dtype=np.float32)) == 5.0
 
 
 def test_tie_and_nan_rules():
@@ -62,8 +71,9 @@ def test_against_golden_fixture():
     z = np.load(GOLDEN)
     index = json.loads(bytes(z["index_json"]).decode())
     assert len(index) > 150
+    assert {e["op"] for e in index} >= {"prod", "norm", "all", "any"}
     for e in index:
-        got = O.reduce(e["op"], z[e["x"]], e["dims"], False, e["correction"])
+        got = O.reduce(e["op"], z[e["x"]], e["dims"], False, e["correction"], e.get("p", 2.0))
         assert same(got, z[e["out"]]), e
 
 
@@ -87,13 +97,19 @@ def test_against_compiled_reference():
                     if dims is None and kd:
                         continue
                     for corr in ((0, 1, 2) if op in ("var", "std") else (1,)):
-                        assert same(O.reduce(op, x, dims, kd, corr), O.ref_reduce(op, x, dims, kd, corr)), \
-                            (shape, dims, op, kd, corr)
+                        for p in ((1.0, 2.0, 3.5, np.inf, -np.inf) if op == "norm" else (2.0,)):
+                            assert same(O.reduce(op, x, dims, kd, corr, p), O.ref_reduce(op, x, dims, kd, corr, p)), \
+                                (shape, dims, op, kd, corr, p)
     x = rng.standard_normal((6, 8, 10)).astype(np.float32)
     for v in (x.transpose(2, 0, 1), x[:, ::2, 1:9], x.transpose(1, 0, 2)[::2]):
         for dims in (None, [0], [1], [2], [0, 2]):
-            for op in ("sum", "mean", "var", "max", "min"):
+            for op in ("sum", "mean", "var", "max", "min", "prod", "norm", "all", "any"):
                 assert same(O.reduce(op, v, dims), O.ref_reduce(op, v, dims)), (v.strides, dims, op)
+    z = rng.integers(0, 2, (5, 6, 7)).astype(np.float32)        # zeros decide all / any / prod
+    z[0, 0, 0] = np.nan
+    for dims in (None, [0], [1], [2], [0, 2]):
+        for op in ("all", "any", "prod"):
+            assert same(O.reduce(op, z, dims), O.ref_reduce(op, z, dims)), (dims, op)
 
 
 @pytest.mark.skipif(not O.have_ref(), reason="the reference's CPU path is not compiled here")
