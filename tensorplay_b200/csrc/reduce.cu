@@ -23,6 +23,7 @@
 #include "host_util.h"
 
 #include <algorithm>
+#include <cmath>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -504,8 +505,17 @@ static int launch_plan(const Plan& pl, const float* in, Epilogue e, float* ov, l
         case ST_NONE:
             return TPB200_OK;
         case ST_ROW_WARP: {
-            unsigned grid = (unsigned)ceil_div(pl.row.rows, 8);
-            row_warp_kernel<Acc><<<grid, 256, 0, st>>>(in, pl.row, e, ov, oi);
+            // rows per CTA: eight, or four where that spreads one wave of CTAs more evenly over the
+            // SMs (4096 rows: 512 CTAs are 3.46 per SM, i.e. 4 on some and 3 on others; 1024 CTAs
+            // are 6.92 per SM)
+            int wpc = 8;
+            {
+                const double sms = (double)sm_count();
+                const double a8 = (double)ceil_div(pl.row.rows, 8) / sms, a4 = (double)ceil_div(pl.row.rows, 4) / sms;
+                if (a4 <= 10.0 && std::ceil(a4) / a4 < std::ceil(a8) / a8 - 0.02) wpc = 4;
+            }
+            unsigned grid = (unsigned)ceil_div(pl.row.rows, wpc);
+            row_warp_kernel<Acc><<<grid, wpc * 32, 0, st>>>(in, pl.row, e, ov, oi);
             TPB_LAUNCH_OK("row_warp_kernel");
             return TPB200_OK;
         }
