@@ -240,6 +240,10 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
                              ("norm p=2", lambda i: tpb.norm(xs[i % n], 2.0, -1, out=ov), 16384),
                              ("all", lambda i: tpb.all(xs[i % n], -1, out=ob), 4096)]:
             cases.append(Case(f"{op} dim=-1 [4096,4096]", fn, inb + outb, 4096, 1, xs))
+        # the same input every step: 64 MiB stays in the 126 MB L2.  Reported beside the cold figures,
+        # never used for a roofline fraction.
+        cases.append(Case("sum dim=-1 [4096,4096] (warm L2: same input every step)", lambda i: tpb.sum(xs[0], -1, out=ov), inb + 16384, 4096, 1, xs))
+        cases.append(Case("argmax dim=-1 [4096,4096] (warm L2: same input every step)", lambda i: tpb.argmax(xs[0], -1, out=oi), inb + 32768, 4096, 1, xs))
     elif workload == "c3":
         a = 64
         xs = [gen_c3(torch, dev, gen, a)]

@@ -10,6 +10,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <ctime>
 #include <limits>
 #include <vector>
 
@@ -111,6 +112,30 @@ int main() {
     // errors keep the reference's type and message
     try { g.sum({2}, false, DType::Undefined); printf("FAIL: no error for a bad dim\n"); ++fails; }
     catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "Dimension out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }
+    // Through-dispatcher latency: TensorPlay's generated Tensor::sum / Tensor::argmax on a [4096,4096]
+    // CUDA tensor, result allocation (the reference's allocator: one cudaMalloc and one cudaFree per
+    // call) and scratch included, against the device time of the kernel alone.
+    {
+        const int64_t N = 4096;
+        Tensor big(std::vector<int64_t>{N, N}, DType::Float32, Device(DeviceType::CUDA, 0));
+        cudaMemset(big.data_ptr(), 0, (size_t)N * N * 4);
+        cudaEvent_t e0, e1;
+        cudaEventCreate(&e0); cudaEventCreate(&e1);
+        for (int which = 0; which < 2; ++which) {
+            for (int i = 0; i < 5; ++i) { Tensor r = which ? big.argmax(std::optional<int64_t>(1), false) : big.sum({1}, false, DType::Undefined); }
+            cudaDeviceSynchronize();
+            const int iters = 200;
+            timespec t0, t1;
+            clock_gettime(CLOCK_MONOTONIC, &t0);
+            for (int i = 0; i < iters; ++i) { Tensor r = which ? big.argmax(std::optional<int64_t>(1), false) : big.sum({1}, false, DType::Undefined); }
+            cudaDeviceSynchronize();
+            clock_gettime(CLOCK_MONOTONIC, &t1);
+            const double wall_us = ((t1.tv_sec - t0.tv_sec) * 1e9 + (t1.tv_nsec - t0.tv_nsec)) / 1e3 / iters;
+            printf("dispatcher_latency %s [4096,4096] dim=1: %.1f us per call through Tensor::%s (allocation included)\n",
+                   which ? "argmax" : "sum", wall_us, which ? "argmax" : "sum");
+        }
+        cudaEventDestroy(e0); cudaEventDestroy(e1);
+    }
     printf("adapter_check: %d checks, %d failures\n", checks, fails);
     fflush(stdout);
     return fails ? 1 : 0;

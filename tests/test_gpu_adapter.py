@@ -19,3 +19,10 @@ def test_tensorplay_dispatches_to_the_new_kernels(cuda):
     r = subprocess.run([BIN], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "0 failures" in r.stdout
+    # the through-dispatcher latency lines (Tensor::sum / Tensor::argmax with allocation) are kept
+    lat = [ln for ln in r.stdout.splitlines() if ln.startswith("dispatcher_latency")]
+    assert len(lat) == 2, r.stdout
+    out_dir = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(out_dir):
+        with open(os.path.join(out_dir, "dispatcher_latency.txt"), "w") as f:
+            f.write("\n".join(lat) + "\n")
