@@ -31,51 +31,6 @@ __device__ __forceinline__ float ld_stream1(const float* p) {
     return v;
 }
 
-// ------------------------------------------------------------------ async bulk copies ------
-// Global -> shared staging with the bulk-copy engine (cp.async.bulk, non-multicast, into the
-// issuing CTA's own shared memory) completing on an mbarrier.  Source and destination must be
-// 16-byte aligned and the size a multiple of 16 bytes.
-__device__ __forceinline__ unsigned smem_u32(const void* p) {
-    return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void fence_mbar_init() {
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after `limit` probes (each probe itself blocks for a hardware-defined
-// short time) and reports false, so a copy that never lands cannot hang the kernel.
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity, int limit = 1 << 20) {
-    for (int i = 0; i < limit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
 // ------------------------------------------------------------------ packed partial ---------
 // One record per (row, slice) between the two passes of a split reduction, and per GPU in the
 // sharded whole-tensor path (it is the all-gather payload).  Field use by family:
