@@ -358,6 +358,19 @@ static int family_of(int op, Family* f) {
     }
 }
 
+
+// Slices per SM of a split reduction: 16 for long inputs (several waves of CTAs even out what the
+// SMs differ in), fewer when that would make a slice shorter than 256 K elements, where the
+// per-slice epilogue starts to show -- most for the variance, whose epilogue is the heaviest.
+// Measured on one B200, 2^28 elements (one GPU's share of 2^31 at eight GPUs): sum 169 / 163 / 165 us,
+// var 219 / 197 / 184 us, max 180 / 170 / 175 us at 16 / 12 / 8 slices per SM; 2^31 elements:
+// 16 per SM is the fastest for all three (var 1227 us against 1290 us at 8).
+static long long split_slices_per_sm(long long elements, int sms) {
+    if (const char* ev = getenv("TPB200_SPLIT_PER_SM")) return std::max(1, atoi(ev));   // experiments
+    const long long per = elements / ((long long)sms * 262144);
+    return std::max(4LL, std::min(16LL, (per + 2) / 4 * 4));
+}
+
 struct Dim { long long size, stride; };
 
 static void push_merged(std::vector<Dim>& v, Dim d) {
@@ -441,7 +454,7 @@ static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64
         // split: few rows, each long enough to feed many CTAs
         int S = 1;
         if (g.nseg == 1 && outs <= 65535) {
-            long long want = ceil_div((long long)sms * 16, outs);
+            long long want = ceil_div((long long)sms * split_slices_per_sm(L * outs, sms), outs);
             long long most = L / 16384;
             S = (int)std::max(1LL, std::min(std::min(want, most), 1LL << 20));
         }
@@ -648,13 +661,13 @@ static void flat_plan(const void* in, int64_t n, Plan* pl) {
     const int sms = sm_count();
     RowGeom& g = pl->row;
     g.rows = 1; g.k1 = 1; g.ks0 = 0; g.ks1 = 0; g.nseg = 1; g.seglen = n; g.seg_stride = 0;
-    long long S = std::max(1LL, std::min((long long)sms * 16, (long long)(n / 16384)));
+    long long S = std::max(1LL, std::min((long long)sms * split_slices_per_sm(n, sms), (long long)(n / 16384)));
     pl->chunk = round_up(ceil_div(std::max<long long>(n, 1), S), 4);
     pl->S = (int)std::max(1LL, ceil_div((long long)n, pl->chunk));
     pl->threads = 512;
     pl->outs = 1;
     pl->count = n;
-    pl->ws_bytes = (size_t)pl->S * sizeof(Packed);
+    pl->ws_bytes = (size_t)std::max(1LL, std::min((long long)sms * 16, (long long)(n / 16384) + 1)) * sizeof(Packed);
     pl->st = ST_ROW_SPLIT;
     (void)in;
 }
