@@ -254,6 +254,7 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
         for op, fn, outb, rows, launches in [
                 ("sum dim=1", lambda i: tpb.sum(xs[0], 1, out=ov1), a * 512 * 4, a * 512, 2),
                 ("mean dim=1", lambda i: tpb.mean(xs[0], 1, out=ov1), a * 512 * 4, a * 512, 2),
+                ("var dim=1", lambda i: tpb.var(xs[0], 1, out=ov1), a * 512 * 4, a * 512, 2),
                 ("max dim=1", lambda i: tpb.max(xs[0], 1, out=ov1), a * 512 * 4, a * 512, 2),
                 ("argmin dim=1", lambda i: tpb.argmin(xs[0], 1, out=oi1), a * 512 * 8, a * 512, 2),
                 ("sum dims=(0,2)", lambda i: tpb.sum(xs[0], [0, 2], out=ov2), 16384, 4096, 1),

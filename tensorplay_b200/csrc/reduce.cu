@@ -397,6 +397,7 @@ static Strategy forced_strategy() {
 
 static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64_t* strides,
                      uint64_t mask, Family fam, Plan* pl) {
+    (void)fam;   // every family plans alike since the variance went to fp32 blocks of four
     if (ndim < 0 || ndim > TPB200_MAX_DIMS)
         return fail(TPB200_ERR_UNSUPPORTED, "tensors of rank %d are not supported (max %d)", ndim, TPB200_MAX_DIMS);
     if (ndim > 0 && (!sizes || !strides)) return fail(TPB200_ERR_INVALID, "sizes/strides must not be NULL");
@@ -493,12 +494,10 @@ static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64
         pl->tiles = (int)ceil_div(pl->I, (long long)pl->tx_n * pl->vec);
         const int ny = 256 / pl->tx_n;
         long long ctas = pl->O * pl->tiles;
-        // sum / extremum: one wave -- as many slices as keep all CTAs resident at once (4 CTAs of 256
-        // threads per SM); measured on [64,4096,512] over dim 1: 2 slices (512 CTAs) 80 us, 5 slices
-        // (1280 CTAs) 95 us.  The variance kernel is bound by the fp64 pipe and its three resident
-        // CTAs per SM, and is fastest with several waves of smaller CTAs (5 slices 111 us, 2: 146 us).
-        long long want = fam == FAM_MOM ? ceil_div((long long)sms * 8, ctas)
-                                        : std::max(1LL, ((long long)sms * 4) / std::max(1LL, ctas));
+        // one wave -- as many slices as keep all CTAs resident at once (4 CTAs of 256 threads per SM);
+        // measured on [64,4096,512] over dim 1: sum 2 slices (512 CTAs) 82 us, 5 slices (1280 CTAs)
+        // 96 us; variance 2 slices 91 us, 5 slices 128 us
+        long long want = std::max(1LL, ((long long)sms * 4) / std::max(1LL, ctas));
         long long most = std::max(1LL, pl->L / ((long long)ny * 8));
         int S = (int)std::max(1LL, std::min(std::min(want, most), 65535LL));
         if (const char* fs = getenv("TPB200_COL_SPLITS")) S = (int)std::max(1LL, std::min<long long>(atoi(fs), most));   // experiments
