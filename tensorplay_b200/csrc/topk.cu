@@ -195,8 +195,8 @@ __device__ __forceinline__ float worst_value() { return LARGEST ? -INFINITY : IN
 // Descending bitonic sort of 32*E words held by one warp, E per lane, lane-major ("blocked":
 // lane l holds positions l*E .. l*E+E-1).  Strides below E are compare-exchanges inside a lane,
 // the others are shuffles; no shared memory and no barrier.
-template <int E>
-__device__ __forceinline__ void warp_sort_desc(unsigned long long (&v)[E], int lane) {
+template <int E, class T = unsigned long long>
+__device__ __forceinline__ void warp_sort_desc(T (&v)[E], int lane) {
 #pragma unroll
     for (int size = 2; size <= 32 * E; size <<= 1) {
 #pragma unroll
@@ -206,7 +206,7 @@ __device__ __forceinline__ void warp_sort_desc(unsigned long long (&v)[E], int l
                 for (int e = 0; e < E; ++e) {
                     if ((e & stride) == 0) {
                         const bool desc = (((lane * E + e) & size) == 0);
-                        unsigned long long x = v[e], y = v[e | stride];
+                        T x = v[e], y = v[e | stride];
                         const bool sw = (x < y) == desc;
                         v[e] = sw ? y : x;
                         v[e | stride] = sw ? x : y;
@@ -218,7 +218,7 @@ __device__ __forceinline__ void warp_sort_desc(unsigned long long (&v)[E], int l
 #pragma unroll
                 for (int e = 0; e < E; ++e) {
                     const bool desc = (((lane * E + e) & size) == 0);
-                    unsigned long long o = __shfl_xor_sync(kFull, v[e], ls);
+                    T o = __shfl_xor_sync(kFull, v[e], ls);
                     const bool keep_max = lower == desc;
                     const bool o_bigger = o > v[e];
                     v[e] = (keep_max == o_bigger) ? o : v[e];
@@ -417,11 +417,11 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     // ((j>>2)*32 + lane)*4 + (j&3) of the tile: float4 number u*32+lane, component c, j = 4u+c.
     auto elem_off = [&](long long off, int j) -> long long { return off + ((j >> 2) * 32 + lane) * 4 + (j & 3); };
 
-    // ---- bootstrap (k <= 256, slice of at least one tile per warp): each warp sorts the 32
+    // ---- bootstrap (k <= 8 per warp, slice of at least one tile per warp): each warp sorts the 32
     // per-lane maxima of its first tile with shuffles; with j = ceil(k/8) every warp holds j lane
     // maxima at or above its j-th largest, so the smallest of the eight j-th largest values has at
     // least 8j >= k elements at or above it: a valid starting threshold.
-    const bool boot = k <= 32 * kStreamWarps && len >= (long long)kStreamWarps * kWarpTile;
+    const bool boot = k <= 8 * kStreamWarps && len >= (long long)kStreamWarps * kWarpTile;
     if (boot) {
         const long long off = (long long)warp * kWarpTile;
         unsigned long long gm[1] = {0ull};
@@ -458,6 +458,59 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
             sh.tau = t;
             sh.mode = (t >> 32) == 0ull ? 2 : 1;
             sh.tvf = key_value<LARGEST>((unsigned)(t >> 32));
+        }
+        __syncthreads();
+    } else if (k <= 128 * kStreamWarps && len >= (long long)kStreamWarps * kWarpTile) {
+        // ---- bootstrap for 8 < k / warps <= 128: the same bound from FOUR values per lane (a
+        // tighter one than the lane maxima give once j approaches 32: measured on [512, 2^20],
+        // k = 512: 432 -> 415 us).  Every
+        // lane keeps the four best of its 32 elements as plain floats (a min/max insertion chain,
+        // NaN ignored), the warp sorts the 128 as keys and offers its j-th largest, j = ceil(k /
+        // warps); the smallest offer has at least warps * j >= k elements at or above its value.  A
+        // lane with fewer than four numbers leaves its start value in the list; if an offer is that
+        // start value the row gets no threshold here and begins by taking everything, as it would
+        // without a bootstrap.  (On [512, 2^20], k = 1024, starting without a threshold costs two of
+        // five cuts and a third of the candidates.)
+        const long long off = (long long)warp * kWarpTile;
+        const float worst = worst_value<LARGEST>();
+        float f0 = worst, f1 = worst, f2 = worst, f3 = worst;
+        auto take = [&](float a) {
+            float hi;
+            hi = LARGEST ? fmaxf(f0, a) : fminf(f0, a); a = LARGEST ? fminf(f0, a) : fmaxf(f0, a); f0 = hi;
+            hi = LARGEST ? fmaxf(f1, a) : fminf(f1, a); a = LARGEST ? fminf(f1, a) : fmaxf(f1, a); f1 = hi;
+            hi = LARGEST ? fmaxf(f2, a) : fminf(f2, a); a = LARGEST ? fminf(f2, a) : fmaxf(f2, a); f2 = hi;
+            f3 = LARGEST ? fmaxf(f3, a) : fminf(f3, a);
+        };
+        if (VEC) {
+            const float* p = slice + off + lane * 4;
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = ld_stream4(p + u * 128);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { take(v[u].x); take(v[u].y); take(v[u].z); take(v[u].w); }
+        } else {
+#pragma unroll 8
+            for (int j = 0; j < 32; ++j) take(ld_stream1(slice + elem_off(off, j) * g.es));
+        }
+        unsigned kk[4] = {rank_key<LARGEST>(f0), rank_key<LARGEST>(f1), rank_key<LARGEST>(f2), rank_key<LARGEST>(f3)};
+        warp_sort_desc<4, unsigned>(kk, lane);
+        const int jr = (k + kStreamWarps - 1) / kStreamWarps - 1;     // 0-based rank among the warp's 128 keys
+        unsigned sel = kk[0];
+#pragma unroll
+        for (int e = 1; e < 4; ++e) sel = (jr & 3) == e ? kk[e] : sel;
+        sel = __shfl_sync(kFull, sel, jr >> 2);
+        if (lane == 0) sh.wmin[warp] = (unsigned long long)sel;
+        __syncthreads();
+        if (tid == 0) {
+            unsigned lo = (unsigned)sh.wmin[0];
+            for (int w8 = 1; w8 < kStreamWarps; ++w8) lo = (unsigned)sh.wmin[w8] < lo ? (unsigned)sh.wmin[w8] : lo;
+            if (lo > rank_key<LARGEST>(worst)) {
+                // exclusive threshold below every element of that key: the low half of a word is never 0
+                const unsigned long long t = (unsigned long long)lo << 32;
+                sh.tau = t;
+                sh.mode = 1;
+                sh.tvf = key_value<LARGEST>(lo);
+            }
         }
         __syncthreads();
     }
