@@ -166,7 +166,7 @@ __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom
 }
 
 // ------------------------------------------------------------------ streaming kernel -------
-// Every warp streams its own tiles (warp w takes warp-tiles w, w+8, ... of the slice) with plain
+// Every warp streams its own tiles (warp w of NW takes warp-tiles w, w+NW, ... of the slice) with plain
 // 128-bit streaming loads, eight per lane and iteration (1024 elements per warp-tile), exactly
 // like the reduction kernels that reach the HBM roofline.  There is no CTA-wide barrier in the
 // streaming loop; the warps of a CTA meet only at a "rendezvous" when the candidate buffer must be
@@ -372,8 +372,8 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     }
     __syncthreads();
 
-    // Rendezvous of the eight warps (no warp is appending while it lasts).  The hardware barrier is
-    // entered only after a software arrival count shows that all eight warps are present: a warp
+    // Rendezvous of the CTA's warps (no warp is appending while it lasts).  The hardware barrier is
+    // entered only after a software arrival count shows that all of them are present: a warp
     // that never comes therefore cannot hang the others -- the wait is bounded, gives up with an
     // error code in the status word, and everybody leaves.  Cuts the buffer, or, once all warps have
     // finished streaming (or after a failure), says so -- the same answer in every thread.
@@ -418,9 +418,9 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     auto elem_off = [&](long long off, int j) -> long long { return off + ((j >> 2) * 32 + lane) * 4 + (j & 3); };
 
     // ---- bootstrap (k <= 8 per warp, slice of at least one tile per warp): each warp sorts the 32
-    // per-lane maxima of its first tile with shuffles; with j = ceil(k/8) every warp holds j lane
-    // maxima at or above its j-th largest, so the smallest of the eight j-th largest values has at
-    // least 8j >= k elements at or above it: a valid starting threshold.
+    // per-lane maxima of its first tile with shuffles; with j = ceil(k / warps) every warp holds j
+    // lane maxima at or above its j-th largest, so the smallest of the warps' j-th largest values
+    // has at least warps * j >= k elements at or above it: a valid starting threshold.
     const bool boot = k <= 8 * kStreamWarps && len >= (long long)kStreamWarps * kWarpTile;
     if (boot) {
         const long long off = (long long)warp * kWarpTile;
