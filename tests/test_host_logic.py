@@ -7,11 +7,15 @@ import torch
 def test_no_cpu_fallback():
     import tensorplay_b200 as tpb
     x = torch.ones(4, 4)
-    for fn in (tpb.sum, tpb.mean, tpb.var, tpb.std, tpb.max, tpb.min, tpb.argmax, tpb.argmin):
+    for fn in (tpb.sum, tpb.mean, tpb.var, tpb.std, tpb.max, tpb.min, tpb.argmax, tpb.argmin, tpb.prod, tpb.norm,
+               tpb.all, tpb.any):
         with pytest.raises(RuntimeError, match="CUDA tensors only"):
             fn(x)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         tpb.topk(x, 2)
+    # norm: the exponents the kernels have; anything else is refused before a tensor is looked at
+    with pytest.raises(NotImplementedError, match="p = 1, 2, inf and -inf"):
+        tpb.norm(x, 3.0)
 
 
 def test_dim_handling_matches_the_reference_rules():
