@@ -25,6 +25,15 @@ __device__ __forceinline__ float4 ld_stream4(const float* p) {
                  : "l"(p));
     return v;
 }
+// The same 128-bit read-only load WITH allocation in L1: for data that the same SM reads again within
+// microseconds (the top-k kernels re-read the few elements that pass their threshold test).
+__device__ __forceinline__ float4 ld_keep4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.nc.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
 __device__ __forceinline__ float ld_stream1(const float* p) {
     float v;
     asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));

@@ -429,7 +429,7 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
             const float* p = slice + off + lane * 4;
             float4 v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = ld_stream4(p + u * 128);
+            for (int u = 0; u < 8; ++u) v[u] = ld_keep4(p + u * 128);
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const unsigned b0 = (unsigned)(begin + off) + (u * 32 + lane) * 4;
@@ -485,7 +485,7 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
             const float* p = slice + off + lane * 4;
             float4 v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = ld_stream4(p + u * 128);
+            for (int u = 0; u < 8; ++u) v[u] = ld_keep4(p + u * 128);
 #pragma unroll
             for (int u = 0; u < 8; ++u) { take(v[u].x); take(v[u].y); take(v[u].z); take(v[u].w); }
         } else {
@@ -517,7 +517,10 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
 
     // ---- streaming loop (warp-autonomous)
     // Hot path: eight 128-bit loads per lane, 32 float compares, one 32-bit mask; nothing else is
-    // kept.  A set bit is a possible candidate: its element is read again by address (an L2 hit),
+    // kept.  The loads allocate in L1 (ld_keep4): with k in the hundreds a tile holds ten or more
+    // candidates, and on inputs far larger than L2 their re-reads went to DRAM when the tile was
+    // loaded past L1 (ncu on [512, 2^20], k = 1024: 6.6 % more DRAM bytes than the input; 477 us
+    // with streaming loads, 439 us with these).  A set bit is a possible candidate: its element is read again by address (an L2 hit),
     // ranked exactly on the 64-bit word, and appended with one shared-memory atomic.
     // `abort`: a rendezvous reported a failure somewhere in the CTA; every warp saw the same answer
     // at the same rendezvous and leaves.
@@ -534,7 +537,7 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
                 const float* p = slice + off + lane * 4;
                 float4 v[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) v[u] = ld_stream4(p + u * 128);
+                for (int u = 0; u < 8; ++u) v[u] = ld_keep4(p + u * 128);
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const bool p0 = LARGEST ? (v[u].x >= tvf) : (v[u].x <= tvf);
