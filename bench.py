@@ -43,6 +43,7 @@ NCU_TRAFFIC_BYTES = {
     "c2": 155_642_880 + 3_520_256,   # profiles/topk_smallk_c2.md
     "c1": 67_143_424 + 418_816,      # profiles/reduce_kernels.md (row_warp_kernel)
     "c3": 536_887_808 + 6_670_848,   # profiles/reduce_kernels.md (col_kernel)
+    "c5": 2_152_235_000 + 14_047_744,  # profiles/topk_stream_c5.md
 }
 
 
