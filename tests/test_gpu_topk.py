@@ -155,6 +155,20 @@ def test_small_k_kernel_geometries(cuda, warps, slices, monkeypatch):
     assert _lib.device_status() == 0
 
 
+def test_large_k_on_strided_rows(cuda):
+    """k in the hundreds along a strided dim: the rendezvous kernel's scalar-load path, with the
+    bootstrap that takes four values per lane, on rows with ties, NaNs and both zeros."""
+    rng = np.random.default_rng(33)
+    x = rng.integers(-50, 50, (40000, 6)).astype(np.float32)
+    x[::13, 2] = np.nan
+    x[5::17, 3] = -0.0
+    for k in (200, 700):
+        check_topk(cuda, x, k, 0, True)
+        check_topk(cuda, x, k, 0, False)
+    y = rng.standard_normal((3, 90001)).astype(np.float32)[:, 1:]      # rows not 16-byte aligned
+    check_topk(cuda, np.ascontiguousarray(y), 1000, -1, True)
+
+
 def test_errors(cuda):
     import torch
     import tensorplay_b200 as tpb
