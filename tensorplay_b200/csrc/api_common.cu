@@ -11,6 +11,11 @@ std::string& last_error_slot() {
     return msg;
 }
 
+bool experiments_on() {
+    static const bool on = getenv("TPB200_EXPERIMENTS") != nullptr;   // read once
+    return on;
+}
+
 int sm_count() {
     static std::mutex mu;
     static int cached[64];

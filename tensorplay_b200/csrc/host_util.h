@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <string>
 
 #include "../../include/tpb200.h"
@@ -45,6 +46,18 @@ inline int cuda_fail(cudaError_t e, const char* what) {
 
 int sm_count();  // SMs of the current device (148 on B200), cached per device
 int* device_status_word();  // device address of the per-device status word (nullptr without a device)
+
+// Planner overrides for experiments and tests (TPB200_FORCE_STRATEGY, TPB200_TOPK_SLICES, ...) are
+// looked up only when TPB200_EXPERIMENTS was set when the library made its first call; without it
+// a call reads no environment variable at all.
+bool experiments_on();
+inline const char* env_str(const char* name) { return experiments_on() ? getenv(name) : nullptr; }
+inline bool env_int(const char* name, int* out) {
+    const char* v = env_str(name);
+    if (!v || !*v) return false;
+    *out = atoi(v);
+    return true;
+}
 
 inline long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 inline long long round_up(long long a, long long b) { return ceil_div(a, b) * b; }

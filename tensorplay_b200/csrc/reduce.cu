@@ -366,7 +366,8 @@ static int family_of(int op, Family* f) {
 // var 219 / 197 / 184 us, max 180 / 170 / 175 us at 16 / 12 / 8 slices per SM; 2^31 elements:
 // 16 per SM is the fastest for all three (var 1227 us against 1290 us at 8).
 static long long split_slices_per_sm(long long elements, int sms) {
-    if (const char* ev = getenv("TPB200_SPLIT_PER_SM")) return std::max(1, atoi(ev));   // experiments
+    int ev = 0;
+    if (env_int("TPB200_SPLIT_PER_SM", &ev)) return std::max(1, ev);
     const long long per = elements / ((long long)sms * 262144);
     return std::max(4LL, std::min(16LL, (per + 2) / 4 * 4));
 }
@@ -382,9 +383,9 @@ static void push_merged(std::vector<Dim>& v, Dim d) {
     }
 }
 
-// Environment override for experiments: TPB200_FORCE_STRATEGY = warp | cta | split | col | generic
+// Override for experiments and tests: TPB200_FORCE_STRATEGY = warp | cta | split | col | generic
 static Strategy forced_strategy() {
-    const char* s = getenv("TPB200_FORCE_STRATEGY");
+    const char* s = env_str("TPB200_FORCE_STRATEGY");
     if (!s) return ST_NONE;
     std::string v(s);
     if (v == "warp") return ST_ROW_WARP;
@@ -500,7 +501,8 @@ static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64
         long long want = std::max(1LL, ((long long)sms * 4) / std::max(1LL, ctas));
         long long most = std::max(1LL, pl->L / ((long long)ny * 8));
         int S = (int)std::max(1LL, std::min(std::min(want, most), 65535LL));
-        if (const char* fs = getenv("TPB200_COL_SPLITS")) S = (int)std::max(1LL, std::min<long long>(atoi(fs), most));   // experiments
+        int fs = 0;
+        if (env_int("TPB200_COL_SPLITS", &fs)) S = (int)std::max(1LL, std::min<long long>(fs, most));
         pl->lchunk = ceil_div(pl->L, S);
         pl->S = (int)ceil_div(pl->L, pl->lchunk);
         if (pl->S > 1) pl->ws_bytes = (size_t)pl->O * pl->S * pl->I * sizeof(Packed);

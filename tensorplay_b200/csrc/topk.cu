@@ -165,6 +165,15 @@ __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom
     return in + a * g.ks0 + b * g.ks1;
 }
 
+// The scanning kernels below also serve as the second launch behind topk_select_kernel: `redo`
+// then holds one flag per row and only flagged rows are processed.  As a dependent launch the
+// kernel may have started before the first one finished: wait for it (a no-op otherwise).
+__device__ __forceinline__ bool row_wanted(const int* redo, long long r) {
+    if (redo == nullptr) return true;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    return *(const volatile int*)(redo + r) != 0;
+}
+
 // ------------------------------------------------------------------ streaming kernel -------
 // Every warp streams its own tiles (warp w of NW takes warp-tiles w, w+NW, ... of the slice) with plain
 // 128-bit streaming loads, eight per lane and iteration (1024 elements per warp-tile), exactly
@@ -347,7 +356,8 @@ enum { kErrRendezvous = 2, kErrRetry = 3, kErrPolling = 4 };
 template <bool LARGEST, bool VEC, int NW>
 __global__ void __launch_bounds__(NW * 32, 32 / NW)
 topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
-                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
+                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status,
+                   const int* __restrict__ redo) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned long long* buf = reinterpret_cast<unsigned long long*>(smem_raw);
     unsigned long long* buf2 = buf + g.B;   // B/2 words: target of the sample-select partition
@@ -355,8 +365,9 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     constexpr int kStreamWarps = NW;
     constexpr int kStreamThreads = NW * 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int s = blockIdx.x;
-    const long long r = blockIdx.y;
+    const int s = (int)(blockIdx.x % (unsigned)g.S);
+    const long long r = (long long)(blockIdx.x / (unsigned)g.S);
+    if (!row_wanted(redo, r)) return;
     const float* row = topk_row(in, g, r);
     const long long begin = (long long)s * g.chunk;
     long long len = g.len - begin;
@@ -753,12 +764,14 @@ __device__ __noinline__ bool cut_chunk(unsigned long long* ring, SmallShared* sh
 template <bool LARGEST, bool VEC, int NW>
 __global__ void __launch_bounds__(NW * 32, NW == 4 ? 7 : (NW == 8 ? 4 : 2))
 topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
-                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
+                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status,
+                   const int* __restrict__ redo) {
     __shared__ __align__(16) unsigned long long ring[kRing];
     __shared__ SmallShared sh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int s = blockIdx.x;
-    const long long r = blockIdx.y;
+    const int s = (int)(blockIdx.x % (unsigned)g.S);
+    const long long r = (long long)(blockIdx.x / (unsigned)g.S);
+    if (!row_wanted(redo, r)) return;
     const float* row = topk_row(in, g, r);
     const long long begin = (long long)s * g.chunk;
     long long len = g.len - begin;
@@ -974,10 +987,12 @@ topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
 template <bool LARGEST, bool FROM_ROW>
 __global__ void __launch_bounds__(kSortThreads)
 topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long long* __restrict__ ws,
-                 int n_items, int N, float* __restrict__ out_val, long long* __restrict__ out_idx) {
+                 int n_items, int N, float* __restrict__ out_val, long long* __restrict__ out_idx,
+                 const int* __restrict__ redo) {
     extern __shared__ __align__(16) unsigned long long buf[];
     const int tid = threadIdx.x, nthr = blockDim.x;
     const long long r = blockIdx.x;
+    if (!row_wanted(redo, r)) return;
     const float* row = topk_row(in, g, r);
     if (FROM_ROW) {
         for (int i = tid; i < N; i += nthr)
@@ -1047,6 +1062,12 @@ topk_merge_pairs_kernel(const float* __restrict__ cv, const long long* __restric
     }
 }
 
+}  // namespace tpb
+
+#include "topk_select.cuh"
+
+namespace tpb {
+
 // ------------------------------------------------------------------ planner ----------------
 enum TopkPath { TK_NONE, TK_SORTROW, TK_STREAM, TK_SMALLK };
 
@@ -1056,9 +1077,69 @@ struct TopkPlan {
     bool vec = false;
     int N = 0;            // sort size of the sort-row path
     int mergeN = 0;       // sort size of the slice merge (S > 1)
-    size_t ws_bytes = 0;
+    size_t ws_bytes = 0;  // whole workspace: redo flags of the select path first, slice survivors after
+    size_t redo_bytes = 0;
     long long out_numel = 0;
+    // select path (topk_select_kernel first, `path` as the second launch for flagged rows)
+    bool select = false;
+    SelGeom sel{};
+    int sel_warps = 16;
 };
+
+// Smallest rank r with P(Poisson(mu) >= r) <= eps.
+static int poisson_rank(double mu, double eps) {
+    double pmf = std::exp(-mu), cdf = 0.0;   // pmf = P(X = i)
+    for (int i = 0; i < 4096; ++i) {
+        if (1.0 - cdf <= eps) return i < 1 ? 1 : i;   // 1 - cdf = P(X >= i)
+        cdf += pmf;
+        pmf *= mu / (double)(i + 1);
+    }
+    return 4096;
+}
+
+// Does the sampled-threshold kernel apply, and with which geometry?  (k, row length, rows only:
+// the values are never looked at on the host.)
+static bool plan_select(long long rows, long long len, long long k, int sms, TopkPlan* pl) {
+    int on = 1;
+    if (env_int("TPB200_TOPK_SELECT", &on) && on == 0) return false;
+    if (k < 1 || k > kMaxStreamK || len < 32 * 1024 || rows > 0x3fffffffLL / kSelMaxCluster) return false;
+    const long long tiles = len / kWarpTile;
+    // candidate buffer: 8 k words, at most 8192 (12 bytes of shared memory per word with cut's
+    // partition target); the CTA width must leave the SM full with that much shared memory per CTA
+    const int cap = (int)std::min<long long>(8192, std::max<long long>(1024, pow2_ceil(8 * k)));
+    int nw = len >= 256 * 1024 ? 16 : (len >= 64 * 1024 ? 8 : 4);
+    if (cap > 2048 && nw < 8) nw = 8;
+    if (cap > 4096) nw = 16;
+    int fw = 0;
+    if (env_int("TPB200_SEL_WARPS", &fw) && (fw == 4 || fw == 8 || fw == 16)) nw = fw;
+    const int per_sm = nw == 4 ? 7 : (nw == 8 ? 4 : 2);
+    // slices per row: the largest cluster that still fits the CTA slots of the GPU once, with at
+    // least eight rounds of tiles per slice
+    int S = 1;
+    while (S < kSelMaxCluster && rows * (2LL * S) <= (long long)sms * per_sm && tiles / (2LL * S) >= 8LL * nw) S *= 2;
+    int fs = 0;
+    if (env_int("TPB200_SEL_SLICES", &fs) && (fs == 1 || fs == 2 || fs == 4 || fs == 8)) S = fs;
+    if (tiles / S < 2LL * nw) return false;
+    const double m = (double)S * nw * kWarpTile;          // sampled elements
+    const double mu = (double)k * m / (double)len;         // of which among the k best, on average
+    int r = poisson_rank(mu, 1e-7);
+    int fr = 0;
+    if (env_int("TPB200_SEL_RANK", &fr) && fr >= 1) r = fr;
+    if (r > std::min(96 * S, 384)) return false;
+    const double expect = (double)r * (double)len / m;     // candidates per row, values all distinct
+    if (expect * 1.5 > (double)cap) return false;
+    SelGeom& sg = pl->sel;
+    sg.S = S;
+    sg.r = r;
+    sg.cap = cap;
+    sg.prefetch = 2;
+    env_int("TPB200_SEL_PREFETCH", &sg.prefetch);
+    sg.prefetch = std::max(0, std::min(8, sg.prefetch));
+    sg.trigger = 1;
+    sg.chunk = round_up(ceil_div(len, S), 4);
+    pl->sel_warps = nw;
+    return true;
+}
 
 static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64_t* strides, int dim,
                      int64_t k, TopkPlan* pl) {
@@ -1113,7 +1194,7 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     g.chunk = len;
     pl->vec = es == 1 && (((uintptr_t)in) & 15) == 0 && g.ks0 % 4 == 0 && g.ks1 % 4 == 0;
 
-    const char* force = getenv("TPB200_FORCE_TOPK");  // "sort" | "stream": experiments only
+    const char* force = env_str("TPB200_FORCE_TOPK");  // "sort" | "stream"
     const bool force_sort = force && std::string(force) == "sort";
     const bool force_stream = force && std::string(force) == "stream";
 
@@ -1124,13 +1205,24 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
         pl->N = std::max(2, pow2_ceil(len));
         return TPB200_OK;
     }
-    if (rows > 65535) {
-        // grid.y limit; such shapes have short rows in practice
-        return fail(TPB200_ERR_UNSUPPORTED, "more than 65535 rows of more than 4096 elements are not supported");
-    }
     const int sms = sm_count();
-    const char* fsk = getenv("TPB200_TOPK_SMALLK");   // "0": experiments with the general kernel
-    if (k <= kSmallK && !(fsk && atoi(fsk) == 0)) {
+    // rows ride on grid.x together with the slices: 2^31 - 1 CTAs per launch
+    auto grid_ok = [&](long long S) { return rows <= 0x7fffffffLL / std::max(1LL, S); };
+    auto finish = [&]() {
+        if (g.S > 1) {
+            pl->mergeN = std::max(2, pow2_ceil((long long)g.S * k));
+            pl->ws_bytes = (size_t)rows * g.S * k * sizeof(unsigned long long);
+        }
+        pl->select = plan_select(rows, len, k, sms, pl);
+        if (pl->select) {
+            pl->redo_bytes = (size_t)round_up(rows * (long long)sizeof(int), 256);
+            pl->ws_bytes += pl->redo_bytes;
+        }
+        return TPB200_OK;
+    };
+    int smallk_on = 1;
+    env_int("TPB200_TOPK_SMALLK", &smallk_on);   // 0: the general kernel for every k
+    if (k <= kSmallK && smallk_on != 0) {
         // barrier-free ring kernel.  CTA width: 16 warps for long rows (one bootstrap and one final
         // step per row, no merge kernel; measured on [256,151936], k = 50: 30.4 us against 38.3 us
         // for 8 warps, 39.5 us for two 8-warp slices and 48.1 us for four 4-warp slices per row),
@@ -1139,12 +1231,16 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
         g.B = kRing;
         g.soft = kChunk;
         g.warps = len >= 64 * 1024 ? 16 : (len >= 16 * 1024 ? 8 : 4);
-        if (const char* fw = getenv("TPB200_TOPK_WARPS")) { int w = atoi(fw); g.warps = w == 16 ? 16 : (w == 8 ? 8 : 4); }   // experiments
+        int fw = 0;
+        if (env_int("TPB200_TOPK_WARPS", &fw)) g.warps = fw == 16 ? 16 : (fw == 8 ? 8 : 4);
         const int per_sm = g.warps == 4 ? 7 : (g.warps == 8 ? 4 : 2);
         long long want = std::max(1LL, (long long)sms * per_sm / rows);
         long long most = std::max(1LL, len / (8LL * g.warps * kWarpTile));
-        long long S = std::min(want, most);
-        if (const char* fs = getenv("TPB200_TOPK_SLICES")) S = std::max(1LL, std::min((long long)atoi(fs), len / ((long long)g.warps * kWarpTile)));
+        // the merge kernel sorts S * k words in shared memory
+        long long cap = std::max(1LL, (long long)kMaxSortRow / k);
+        long long S = std::min(std::min(want, most), cap);
+        int fs = 0;
+        if (env_int("TPB200_TOPK_SLICES", &fs)) S = std::max(1LL, std::min(std::min((long long)fs, cap), len / ((long long)g.warps * kWarpTile)));
         g.chunk = round_up(ceil_div(len, S), 4);
         g.S = (int)ceil_div(len, g.chunk);
         // the last slice must still hold one tile per warp for the bootstrap
@@ -1154,23 +1250,21 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
             g.S = (int)ceil_div(len, g.chunk);
         }
         if (len < (long long)g.warps * kWarpTile) { g.warps = 4; }   // len > 4096 here, so four tiles exist
-        if (g.S > 1) {
-            pl->mergeN = std::max(2, pow2_ceil((long long)g.S * k));
-            pl->ws_bytes = (size_t)rows * g.S * k * sizeof(unsigned long long);
-        }
-        return TPB200_OK;
+        if (!grid_ok(g.S)) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
+        return finish();
     }
     pl->path = TK_STREAM;
     g.B = pow2_ceil(std::max<long long>(4 * k, 1024));
     // first cut early: handling a candidate costs far more than skipping an element, and only a cut
     // tightens the threshold (measured on [256,151936], k = 50: 320 words beats 160 and 1024)
     g.soft = (int)std::min<long long>(g.B / 2, std::max<long long>(320, 3 * k));
-    if (const char* fb = getenv("TPB200_TOPK_B")) g.B = std::max(g.B, pow2_ceil(atoi(fb)));                        // experiments
-    if (const char* fso = getenv("TPB200_TOPK_SOFT")) g.soft = std::min(g.B - 1, std::max(atoi(fso), (int)k + 1));   // experiments
+    int fb = 0, fso = 0, fw = 0;
+    if (env_int("TPB200_TOPK_B", &fb)) g.B = std::max(g.B, pow2_ceil(fb));
+    if (env_int("TPB200_TOPK_SOFT", &fso)) g.soft = std::min(g.B - 1, std::max(fso, (int)k + 1));
     // CTA width: 16 warps for long rows (half as many bootstraps / cuts as two 8-warp slices and,
     // with one CTA per row, no merge kernel), 8 warps for rows below 64 K elements.
     g.warps = len >= 64 * 1024 ? 16 : 8;
-    if (const char* fw = getenv("TPB200_TOPK_WARPS")) g.warps = atoi(fw) == 16 ? 16 : 8;   // experiments
+    if (env_int("TPB200_TOPK_WARPS", &fw)) g.warps = fw == 16 ? 16 : 8;
     // slices: fill the CTA slots of the GPU once, never overshoot them; each slice at least eight
     // rounds of all warps and at least 8k long
     const int slots = sms * (g.warps == 16 ? 2 : 4);
@@ -1181,22 +1275,77 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     // two slices per row are the most that still pay off
     if (k > 256) want = std::min(want, 2LL);
     long long S = std::max(1LL, std::min(std::min(want, most), cap));
-    const char* fs = getenv("TPB200_TOPK_SLICES");
-    if (fs) S = std::max(1LL, std::min((long long)atoi(fs), cap));
+    int fs = 0;
+    if (env_int("TPB200_TOPK_SLICES", &fs)) S = std::max(1LL, std::min((long long)fs, cap));
     g.chunk = round_up(ceil_div(len, S), 4);
     g.S = (int)ceil_div(len, g.chunk);
-    if (g.S > 1) {
-        pl->mergeN = std::max(2, pow2_ceil((long long)g.S * k));
-        pl->ws_bytes = (size_t)rows * g.S * k * sizeof(unsigned long long);
-    }
-    return TPB200_OK;
+    if (!grid_ok(g.S)) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
+    return finish();
 }
 
 template <class K>
 static int allow_smem(K kernel, size_t bytes) {
-    if (bytes + 4096 > 48 * 1024) {   // static shared memory counts against the 48 KB default too
+    if (bytes + 8192 > 48 * 1024) {   // static shared memory counts against the 48 KB default too
         TPB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
+    return TPB200_OK;
+}
+
+// One launch through cudaLaunchKernelEx: `cluster` > 1 makes clusters of that many CTAs along x,
+// `dependent` lets the kernel start before the previous kernel of the stream has finished (it must
+// then call griddepcontrol.wait before it touches memory: row_wanted() does).
+template <class... KArgs, class... Args>
+static cudaError_t launch_ex(void (*kernel)(KArgs...), unsigned grid, int threads, size_t smem, cudaStream_t st,
+                             int cluster, bool dependent, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    unsigned na = 0;
+    if (cluster > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)cluster;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (dependent) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+static bool dependent_launch_on() {
+    int v = 1;
+    env_int("TPB200_PDL", &v);
+    return v != 0;
+}
+
+template <bool LARGEST>
+static int select_launch(const TopkPlan& pl, const float* in, float* ov, long long* oi, int* redo, cudaStream_t st) {
+    const TopkGeom& g = pl.g;
+    SelGeom sg = pl.sel;
+    sg.trigger = dependent_launch_on() ? 1 : 0;
+    const size_t sm = (size_t)sg.cap * 12;
+    const unsigned grid = (unsigned)(g.rows * sg.S);
+    const int nw = pl.sel_warps;
+    cudaError_t e = cudaSuccess;
+#define TPB_LAUNCH_SELECT(V, W)                                                                           \
+    do {                                                                                                  \
+        int rc = allow_smem(topk_select_kernel<LARGEST, V, W>, sm);                                       \
+        if (rc) return rc;                                                                                \
+        e = launch_ex(topk_select_kernel<LARGEST, V, W>, grid, W * 32, sm, st, sg.S, false, in, g, sg, ov, oi, redo); \
+    } while (0)
+    if (pl.vec) { if (nw == 16) TPB_LAUNCH_SELECT(true, 16); else if (nw == 8) TPB_LAUNCH_SELECT(true, 8); else TPB_LAUNCH_SELECT(true, 4); }
+    else        { if (nw == 16) TPB_LAUNCH_SELECT(false, 16); else if (nw == 8) TPB_LAUNCH_SELECT(false, 8); else TPB_LAUNCH_SELECT(false, 4); }
+#undef TPB_LAUNCH_SELECT
+    if (e != cudaSuccess) return cuda_fail(e, "topk_select_kernel");
     return TPB200_OK;
 }
 
@@ -1210,42 +1359,53 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
         if (rc) return rc;
         int threads = std::min(kSortThreads, std::max(32, pl.N / 2));
         if (g.rows > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
-        topk_sort_kernel<LARGEST, true><<<(unsigned)g.rows, threads, sm, st>>>(in, g, nullptr, (int)g.len, pl.N, ov, oi);
+        topk_sort_kernel<LARGEST, true><<<(unsigned)g.rows, threads, sm, st>>>(in, g, nullptr, (int)g.len, pl.N, ov, oi, nullptr);
         TPB_LAUNCH_OK("topk_sort_kernel");
         return TPB200_OK;
     }
-    dim3 grid((unsigned)g.S, (unsigned)g.rows);
+    // select path: the sampled-threshold kernel first; the scanning kernels below then redo only
+    // the rows it flagged (as a dependent launch: their CTAs are resident when the first kernel ends)
+    int* redo = nullptr;
+    if (pl.select) {
+        redo = (int*)ws;
+        ws = (unsigned char*)ws + pl.redo_bytes;
+        int rc = select_launch<LARGEST>(pl, in, ov, oi, redo, st);
+        if (rc) return rc;
+    }
+    const bool dep = redo != nullptr && dependent_launch_on();
+    const unsigned grid = (unsigned)(g.rows * g.S);
     unsigned long long* w = g.S > 1 ? (unsigned long long*)ws : nullptr;
     int* status = device_status_word();
     const int threads = g.warps * 32;
+    cudaError_t e = cudaSuccess;
     if (pl.path == TK_SMALLK) {
-#define TPB_LAUNCH_SMALLK(V, W) topk_smallk_kernel<LARGEST, V, W><<<grid, threads, 0, st>>>(in, g, w, ov, oi, status)
+#define TPB_LAUNCH_SMALLK(V, W) e = launch_ex(topk_smallk_kernel<LARGEST, V, W>, grid, threads, 0, st, 1, dep, in, g, w, ov, oi, status, (const int*)redo)
         if (pl.vec) {
             if (g.warps == 16) TPB_LAUNCH_SMALLK(true, 16); else if (g.warps == 8) TPB_LAUNCH_SMALLK(true, 8); else TPB_LAUNCH_SMALLK(true, 4);
         } else {
             if (g.warps == 16) TPB_LAUNCH_SMALLK(false, 16); else if (g.warps == 8) TPB_LAUNCH_SMALLK(false, 8); else TPB_LAUNCH_SMALLK(false, 4);
         }
 #undef TPB_LAUNCH_SMALLK
-        TPB_LAUNCH_OK("topk_smallk_kernel");
+        if (e != cudaSuccess) return cuda_fail(e, "topk_smallk_kernel");
     } else {
-    const size_t sm = (size_t)g.B * 12;
+        const size_t sm = (size_t)g.B * 12;
 #define TPB_LAUNCH_STREAM(V, W)                                                                          \
     do {                                                                                                 \
         int rc = allow_smem(topk_stream_kernel<LARGEST, V, W>, sm);                                      \
         if (rc) return rc;                                                                               \
-        topk_stream_kernel<LARGEST, V, W><<<grid, threads, sm, st>>>(in, g, w, ov, oi, status);          \
+        e = launch_ex(topk_stream_kernel<LARGEST, V, W>, grid, threads, sm, st, 1, dep, in, g, w, ov, oi, status, (const int*)redo); \
     } while (0)
-    if (pl.vec) { if (g.warps == 16) TPB_LAUNCH_STREAM(true, 16); else TPB_LAUNCH_STREAM(true, 8); }
-    else        { if (g.warps == 16) TPB_LAUNCH_STREAM(false, 16); else TPB_LAUNCH_STREAM(false, 8); }
+        if (pl.vec) { if (g.warps == 16) TPB_LAUNCH_STREAM(true, 16); else TPB_LAUNCH_STREAM(true, 8); }
+        else        { if (g.warps == 16) TPB_LAUNCH_STREAM(false, 16); else TPB_LAUNCH_STREAM(false, 8); }
 #undef TPB_LAUNCH_STREAM
-    TPB_LAUNCH_OK("topk_stream_kernel");
+        if (e != cudaSuccess) return cuda_fail(e, "topk_stream_kernel");
     }
     if (g.S > 1) {
         size_t msm = (size_t)pl.mergeN * 8;
         int rc = allow_smem(topk_sort_kernel<LARGEST, false>, msm);
         if (rc) return rc;
-        int threads = std::min(kSortThreads, std::max(32, pl.mergeN / 2));
-        topk_sort_kernel<LARGEST, false><<<(unsigned)g.rows, threads, msm, st>>>(in, g, w, g.S * (int)g.k, pl.mergeN, ov, oi);
+        int mthreads = std::min(kSortThreads, std::max(32, pl.mergeN / 2));
+        topk_sort_kernel<LARGEST, false><<<(unsigned)g.rows, mthreads, msm, st>>>(in, g, w, g.S * (int)g.k, pl.mergeN, ov, oi, (const int*)redo);
         TPB_LAUNCH_OK("topk_sort_kernel(merge)");
     }
     return TPB200_OK;

@@ -3,6 +3,10 @@ import sys
 
 import pytest
 
+# the planner overrides that some tests set (TPB200_TOPK_SLICES, TPB200_FORCE_STRATEGY, ...) are only
+# honoured when this switch is in the environment at the library's first call
+os.environ.setdefault("TPB200_EXPERIMENTS", "1")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

@@ -73,11 +73,32 @@ def test_workspace_planner(lib):
     # column reduction over dim 1 of [64, 4096, 512]: records for [64, S, 512]
     n = lib.tpb200_reduce_workspace_bytes(0, 0, 3, i64([64, 4096, 512]), i64([4096 * 512, 512, 1]), 1 << 1)
     assert n % (64 * 512 * P) == 0
-    # top-k: one slice per row needs no scratch; several slices need S*k words per row
+    # top-k: one slice per row needs no scratch; several slices need S*k words per row (the select
+    # path adds one redo flag per row in front, rounded up to 256 bytes)
     assert lib.tpb200_topk_workspace_bytes(0, 2, i64([4, 1000]), i64([1000, 1]), 1, 5) == 0
     n = lib.tpb200_topk_workspace_bytes(0, 2, i64([8, 1 << 22]), i64([1 << 22, 1]), 1, 64)
-    assert n > 0 and n % (8 * 64 * 8) == 0
+    assert n > 256 and (n - 256) % (8 * 64 * 8) == 0
     # too small a workspace is refused before any launch
     rc = lib.tpb200_reduce(0, ctypes.c_void_p(16), 0, 1, i64([1 << 31]), i64([1]), 0, -1, 1,
                            ctypes.c_void_p(16), None, ctypes.c_void_p(256), 8, None)
     assert rc == _lib.ERR_WORKSPACE
+
+
+def test_topk_slices_fit_the_merge_kernel(lib, monkeypatch):
+    """One very long row, k <= 64: the number of slices times k must stay within what the merge
+    kernel sorts in shared memory (16384 words), whatever the row length."""
+    from tensorplay_b200 import _lib
+    i64 = _lib.i64_array
+    monkeypatch.setenv("TPB200_TOPK_SELECT", "0")      # the scanning kernels' own workspace only
+    for n in (1 << 22, 1 << 25, 1 << 26, 1 << 28, (1 << 31) + 5):
+        for k in range(1, 65):
+            nb = lib.tpb200_topk_workspace_bytes(0, 1, i64([n]), i64([1]), 0, k)
+            words = nb // 8
+            assert words % k == 0 and words <= 16384, (n, k, words)
+            mergeN = 2
+            while mergeN < words:
+                mergeN *= 2
+            assert mergeN * 8 <= 227 * 1024
+    # rows ride on grid.x: more than 65535 long rows plan without an error
+    assert lib.tpb200_topk(None, 0, 2, i64([70000, 8192]), i64([8192, 1]), 1, 5, 1, 1, None, None, None, 0, None) == _lib.ERR_INVALID
+    assert b"input pointer is NULL" in lib.tpb200_last_error()

@@ -8,6 +8,14 @@ from util import assert_bits_equal, assert_index_equal, config2, config5
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["select", "scan"], autouse=True)
+def topk_path(request, monkeypatch):
+    """Every test runs twice: with the sampled-threshold kernel in front (the default for long rows;
+    the scanning kernels then only redo the rows it flags) and with the scanning kernels alone."""
+    monkeypatch.setenv("TPB200_TOPK_SELECT", "1" if request.param == "select" else "0")
+    return request.param
+
+
 def check_topk(device, x, k, dim=-1, largest=True, what="", oracle="heap"):
     import torch
     import tensorplay_b200 as tpb
@@ -54,7 +62,7 @@ def test_streaming_path(cuda, k):
 
 @pytest.mark.parametrize("slices", ["1", "2", "5"])
 def test_streaming_slices(cuda, slices, monkeypatch):
-    monkeypatch.setenv("TPB200_TOPK_SLICES", slices)
+    monkeypatch.setenv("TPB200_TOPK_SLICES", slices)   # slices of the scanning kernels (second launch / alone)
     rng = np.random.default_rng(24)
     x = rng.standard_normal((5, 300001)).astype(np.float32)
     for k in (50, 1024):
@@ -183,15 +191,108 @@ def test_errors(cuda):
         tpb.topk(torch.ones(2, 100000, device=cuda), 3000)
 
 
-def test_config2_logits(cuda):
-    """BASELINE config 2: [256, 151936] N(0, 2), 64 planted +8.0 per row, k = 50."""
+@pytest.mark.parametrize("warps,slices", [("16", "1"), ("16", "2"), ("8", "4"), ("4", "8"), ("8", "1")])
+def test_select_kernel_geometries(cuda, warps, slices, monkeypatch, topk_path):
+    """The sampled-threshold kernel with one CTA per row and with clusters of 2, 4 and 8 CTAs per row
+    (candidates merged through distributed shared memory), on rows it can finish itself and on rows
+    it must hand to the second launch: ascending rows (the sample says nothing about the rest),
+    all-equal rows (every element is a candidate) and rows with fewer numbers than k."""
+    if topk_path != "select":
+        pytest.skip("select path only")
+    from tensorplay_b200 import _lib
+    monkeypatch.setenv("TPB200_SEL_WARPS", warps)
+    monkeypatch.setenv("TPB200_SEL_SLICES", slices)
+    rng = np.random.default_rng(41)
+    n = 300007
+    x = rng.standard_normal((6, n)).astype(np.float32)
+    x[1, ::3] = 2.5                                    # 100 k ties far above the threshold: overflow, redone
+    x[2] = np.sort(x[2])                               # ascending
+    x[3] = rng.integers(0, 1000, n).astype(np.float32)  # tie-heavy
+    x[4, 5000:] = np.nan                               # numbers only at the start
+    x[5, :] = np.nan
+    x[5, 123456] = 1.0                                 # fewer numbers than k
+    for k in (1, 50, 64, 300, 1024, 2048):
+        for largest in (True, False):
+            check_topk(cuda, x, k, -1, largest, what=f"select warps={warps} S={slices}")
+    y = rng.standard_normal((3, 100003)).astype(np.float32)[:, 3:]     # rows not 16-byte aligned: scalar loads
+    check_topk(cuda, np.ascontiguousarray(y), 40, -1, True)
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("rank,pdl", [("1", "1"), ("1", "0"), ("90", "1")])
+def test_select_rows_redone_by_second_launch(cuda, rank, pdl, monkeypatch, topk_path):
+    """A threshold taken too high (rank 1: the sample's maximum) leaves fewer than k candidates in
+    every row, one taken too low overflows the candidate buffer: either way the row is flagged and the
+    second launch produces it -- as a dependent launch and as an ordinary one."""
+    if topk_path != "select":
+        pytest.skip("select path only")
+    from tensorplay_b200 import _lib
+    monkeypatch.setenv("TPB200_SEL_RANK", rank)
+    monkeypatch.setenv("TPB200_PDL", pdl)
+    rng = np.random.default_rng(42)
+    x = rng.standard_normal((9, 200000)).astype(np.float32)
+    for k in (50, 700):
+        check_topk(cuda, x, k, -1, True, what=f"rank={rank} pdl={pdl}")
+        check_topk(cuda, x, k, -1, False, what=f"rank={rank} pdl={pdl}")
+    assert _lib.device_status() == 0
+
+
+def test_select_many_calls_in_one_graph(cuda, topk_path):
+    """Several calls captured in one CUDA graph (cluster launches and the dependent second launch as
+    graph nodes) give the same bits as eager calls."""
+    if topk_path != "select":
+        pytest.skip("select path only")
+    import torch
+    import tensorplay_b200 as tpb
+    rng = np.random.default_rng(43)
+    xs = [torch.from_numpy(rng.standard_normal((16, 150000)).astype(np.float32)).to(cuda) for _ in range(3)]
+    xs[1][3] = torch.sort(xs[1][3]).values          # one row of one input goes through the second launch
+    eager = [tpb.topk(x, 50) for x in xs]
+    outs = [(torch.empty(16, 50, device=cuda), torch.empty(16, 50, dtype=torch.int64, device=cuda)) for _ in xs]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for x, o in zip(xs, outs):
+            tpb.topk(x, 50, out=o)                  # warm-up outside the capture (workspace allocation)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for x, o in zip(xs, outs):
+                tpb.topk(x, 50, out=o)
+        for o in outs:
+            o[0].zero_(); o[1].zero_()
+        graph.replay()
+        stream.synchronize()
+    for (ev, ei), (gv, gi) in zip(eager, outs):
+        assert torch.equal(ei, gi) and torch.equal(ev.view(torch.int32), gv.view(torch.int32))
+
+
+def test_one_long_row_small_k(cuda):
+    """One row of 2^26 elements, k = 56 and 64: the slices of the ring kernel are limited by what
+    the merge kernel can sort in shared memory."""
+    rng = np.random.default_rng(44)
+    x = rng.standard_normal((1, 1 << 26)).astype(np.float32)
+    for k in (56, 64):
+        check_topk(cuda, x, k, -1, True)
+        check_topk(cuda, x, k, -1, False)
+
+
+def test_more_rows_than_a_grid_dimension(cuda):
+    """70 000 rows of 4100 elements: rows ride on grid.x, so the 65 535 limit of grid.y is gone."""
+    rng = np.random.default_rng(45)
+    x = rng.integers(0, 50, (70000, 4100)).astype(np.float32)
+    check_topk(cuda, x, 5, -1, True)
+    check_topk(cuda, x, 100, -1, False)
+
+
+def test_logits_256x151936_k50(cuda):
+    """[256, 151936] N(0, 2) with 64 planted +8.0 per row, k = 50 (the headline shape, full size)."""
     x = config2()
     check_topk(cuda, x, 50, -1, True)
 
 
-def test_config5_tie_heavy_rows(cuda):
-    """BASELINE config 5 at 64 of its 512 rows (one GPU's share at 8 GPUs; same generator and seed):
-    integers 0..999 as float, k = 1024, both directions."""
-    x = config5(rows=64)
+def test_tie_heavy_512x1048576_k1024(cuda):
+    """[512, 1048576] integers 0..999 as float, k = 1024, both directions, all 512 rows: the answer is
+    decided by the tie rule alone."""
+    x = config5()
     check_topk(cuda, x, 1024, -1, True)
     check_topk(cuda, x, 1024, -1, False)
