@@ -18,7 +18,12 @@ The JSON line reports
                        memory: host->device copy + kernels + device->host copy of the results;
   roofline             algorithmic bytes / average kernel time against the measured copy peak;
   cpu_baseline         the CPU checker timed on the host cores (N = 1 only);
-  suite                every other benchmark configuration, measured the same way (not the headline).
+  suite                every other benchmark configuration, measured the same way (not the headline);
+                       at N = 1 every reduction carries `cpu_reference`: the reference's own CPU kernel
+                       for that operator (compiled from its sources, one host thread) timed beside it;
+  parity               untimed: the sharded whole-tensor reductions (fused peer exchange and all-gather),
+                       the global top-k and row-sharded top-k on small seeded inputs, every rank's
+                       result compared with the CPU checker -- "ok" only if all ranks agree with it.
 """
 from __future__ import annotations
 
@@ -34,16 +39,16 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 L2_BYTES = 126 * (1 << 20)
-FALLBACK_PEAK_GBS = 6650.0   # earlier measurement on this pool; used only without MEASURED_PEAKS.json
+FALLBACK_PEAK_GBS = 6650.0   # used only when MEASURED_PEAKS.json is absent
 NOMINAL_PEAK_GBS = 8000.0
 
 # DRAM traffic per launch of the dominant kernel from one ncu capture (dram__bytes_read.sum +
-# dram__bytes_write.sum; summaries under profiles/).  None where no capture exists.
+# dram__bytes_write.sum).  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    "c2": 155_642_880 + 3_520_256,   # profiles/topk_smallk_c2.md
-    "c1": 67_143_424 + 418_816,      # profiles/reduce_kernels.md (row_warp_kernel)
-    "c3": 536_887_808 + 6_670_848,   # profiles/reduce_kernels.md (col_kernel)
-    "c5": 2_152_235_000 + 14_047_744,  # profiles/topk_stream_c5.md
+    "c2": None,                      # topk_select_kernel: filled in from the capture of this kernel
+    "c1": 67_143_424 + 418_816,      # row_warp_kernel
+    "c3": 536_887_808 + 6_670_848,   # col_kernel
+    "c5": None,
 }
 
 
@@ -221,7 +226,7 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
         ov = torch.empty(256, 50, device=dev)
         oi = torch.empty(256, 50, dtype=torch.int64, device=dev)
         b = 256 * 151936 * 4 + 256 * 50 * 12
-        launches = 1 + (tpb._lib.lib().tpb200_topk_workspace_bytes(0, 2, tpb._lib.i64_array([256, 151936]), tpb._lib.i64_array([151936, 1]), 1, 50) > 0)
+        launches = tpb._lib.topk_plan_info([256, 151936], [151936, 1], 1, 50)["launches"]
         cases.append(Case("topk k=50 [256,151936]", lambda i: tpb.topk(xs[i % n], 50, -1, True, True, out=(ov, oi)), b, 256, launches, xs))
     elif workload == "c1":
         n = copies_to_exceed_l2(4096 * 4096 * 4)
@@ -290,10 +295,11 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
         ov = torch.empty(r1 - r0, 1024, device=dev)
         oi = torch.empty(r1 - r0, 1024, dtype=torch.int64, device=dev)
         b = (r1 - r0) * ((1 << 20) * 4 + 1024 * 12)
+        launches = tpb._lib.topk_plan_info([r1 - r0, 1 << 20], [1 << 20, 1], 1, 1024)["launches"]
         for largest in (True, False):
             cases.append(Case(f"topk k=1024 largest={largest} [512,1048576] / {world} GPUs",
                               (lambda lg: (lambda i: tpb.topk(x, 1024, -1, lg, True, out=(ov, oi))))(largest),
-                              b, r1 - r0, 1, [x]))
+                              b, r1 - r0, launches, [x]))
     else:
         raise ValueError(workload)
     return cases
@@ -359,9 +365,139 @@ def cpu_topk_c2(threads: int, reps: int = 3, rows: int = 256):
     return nbytes / best / 1e9, best * 1e3, len(blocks)
 
 
+def _best_of(fn, reps):
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def cpu_reference_suite(world: int):
+    """The reference's own CPU reductions (its ReductionKernels.cpp compiled as it stands into
+    oracle/_ref/libtpref.so) timed per operator on ONE host thread -- the reference's CPU kernels are
+    single-threaded by construction.  Same shapes and distributions as the GPU suite; the whole-tensor
+    case runs on 2^28 of the 2^31 elements (GB/s does not depend on the length; a full pass would take
+    minutes and 24 GiB for var).  Returns {suite entry name: cpu_reference dict}."""
+    import numpy as np
+    from oracle import oracle as O
+
+    if not O.have_ref():
+        return {}
+    cores = os.cpu_count() or 1
+    out = {}
+
+    def entry(nbytes, secs, sample):
+        return {"value": round(nbytes / secs / 1e9, 3), "unit": "GB/s", "ms": round(secs * 1e3, 2), "cores": 1,
+                "host_threads_available": cores, "kind": "reference", "sample": sample}
+
+    x = np.random.default_rng(0).standard_normal((4096, 4096), dtype=np.float32)
+    t = {op: _best_of(lambda op=op: O.ref_reduce(op, x, [1]), 3) for op in ("sum", "mean", "var", "max", "argmax")}
+    for op in ("sum", "mean", "var", "max", "argmax"):
+        out[f"{op} dim=-1 [4096,4096]"] = entry(x.nbytes, t[op], "full [4096,4096], best of 3")
+    out["max+argmax dim=-1 [4096,4096]"] = entry(x.nbytes, t["max"] + t["argmax"], "full [4096,4096]: max.dim + argmax, two passes (the reference has no fused form)")
+    del x
+    x = np.random.default_rng(2).uniform(-1.0, 1.0, (64, 4096, 512)).astype(np.float32)
+    for name, op, dims in [("sum dim=1", "sum", [1]), ("mean dim=1", "mean", [1]), ("var dim=1", "var", [1]),
+                           ("max dim=1", "max", [1]), ("argmin dim=1", "argmin", [1]),
+                           ("sum dims=(0,2)", "sum", [0, 2]), ("std dims=(0,2)", "std", [0, 2])]:
+        secs = _best_of(lambda: O.ref_reduce(op, x, dims), 2)
+        out[f"{name} [64,4096,512]"] = entry(x.nbytes, secs, "full [64,4096,512], best of 2")
+    del x
+    n = 1 << 28
+    rng = np.random.default_rng(3)
+    x = np.empty(n, dtype=np.float32)
+    for s0 in range(0, n, 1 << 24):
+        v = rng.uniform(-1.0, 1.0, 1 << 24).astype(np.float32)
+        pos = rng.choice(1 << 24, (1 << 24) // 100, replace=False)
+        v[pos] = np.where(rng.integers(0, 2, pos.size) == 0, np.float32(1e4), np.float32(-1e4))
+        x[s0:s0 + (1 << 24)] = v
+    for op in ("sum", "mean", "var", "max", "argmax"):
+        secs = _best_of(lambda: O.ref_reduce(op, x, None), 2)
+        out[f"{op} whole tensor 2^31 / {world} GPUs"] = entry(x.nbytes, secs, "2^28 of the 2^31 elements (1/8 of the tensor; time for the full tensor = 8 x ms), best of 2")
+    return out
+
+
+def parity_check(torch, tpb, dev, rank: int, world: int) -> str:
+    """Untimed correctness evidence at this number of ranks: every rank compares what the sharded
+    paths return with the CPU checker on the same seeded data.  "ok" or the first differences."""
+    import numpy as np
+    import torch.distributed as dist
+    from oracle import oracle as O
+
+    bad = []
+    n = (1 << 24) + 5 * world + 3
+    rng = np.random.default_rng(99)
+    x = rng.uniform(-1.0, 1.0, n).astype(np.float32)
+    pos = rng.choice(n, n // 100, replace=False)
+    x[pos] = np.where(rng.integers(0, 2, pos.size) == 0, np.float32(1e4), np.float32(-1e4))
+    x[n - 300] = 3e4          # the maximum sits in the last partition ...
+    x[n // 3] = 3e4           # ... and ties with an earlier element: the lower index must win
+    x[n // 2 + 1] = -3e4
+    a, b = tpb.flat_partition(n, rank, world)
+    local = torch.from_numpy(x[a:b].copy()).to(dev)
+    truth = {op: float(O.truth64(op, x)) for op in ("sum", "mean", "var", "std")}
+    exact = {"max": float(x.max()), "argmax": int(np.argmax(x)), "min": float(x.min()), "argmin": int(np.argmin(x))}
+    reducers = [("all-gather", tpb.ShardedReducer(dev))]
+    try:
+        reducers.append(("fused exchange", tpb.ShardedReducer(dev, fused=True)))
+    except Exception as e:
+        bad.append(f"fused exchange unavailable: {str(e)[:80]}")
+    for tag, red in reducers:
+        for rep in range(2):
+            for op in ("sum", "mean", "var", "std"):
+                v, _ = red.reduce(op, local, a, n)
+                g = float(v.item())
+                if not abs(g - truth[op]) <= 1e-5 * abs(truth[op]):
+                    bad.append(f"{tag} {op}: {g!r} vs float64 {truth[op]!r}")
+            v, i = red.reduce("max_argmax", local, a, n)
+            if float(v.item()) != exact["max"] or int(i.item()) != exact["argmax"]:
+                bad.append(f"{tag} max_argmax: ({v.item()}, {i.item()}) vs ({exact['max']}, {exact['argmax']})")
+            v, i = red.reduce("min_argmin", local, a, n)
+            if float(v.item()) != exact["min"] or int(i.item()) != exact["argmin"]:
+                bad.append(f"{tag} min_argmin: ({v.item()}, {i.item()}) vs ({exact['min']}, {exact['argmin']})")
+    # global top-k over the flat sharded tensor: tie-heavy, so global index order decides
+    y = np.random.default_rng(98).integers(0, 2000, n).astype(np.float32)
+    ylocal = torch.from_numpy(y[a:b].copy()).to(dev)
+    red = reducers[0][1]
+    for k, largest in ((64, True), (1024 if 1024 * world <= 8192 else 8192 // world, False)):
+        tv, ti = red.topk(ylocal, k, a, largest)
+        wv, wi = O.topk(y[None, :], k, -1, largest)
+        if not np.array_equal(ti.cpu().numpy(), wi[0]) or not np.array_equal(tv.cpu().numpy().view(np.uint32), wv[0].view(np.uint32)):
+            bad.append(f"global top-k k={k} largest={largest} differs")
+    # row-sharded top-k on this rank's rows (the headline shape and the tie-heavy shape)
+    rr = np.random.default_rng(1000 + rank)
+    z = rr.normal(0.0, 2.0, (4, 151936)).astype(np.float32)
+    for r in range(4):
+        z[r, rr.choice(151936, 64, replace=False)] = np.float32(8.0)
+    v, i = tpb.topk(torch.from_numpy(z).to(dev), 50, -1, True, True)
+    wv, wi = O.topk(z, 50, -1, True)
+    if not np.array_equal(i.cpu().numpy(), wi) or not np.array_equal(v.cpu().numpy().view(np.uint32), wv.view(np.uint32)):
+        bad.append("top-k k=50 [4,151936] differs")
+    z = rr.integers(0, 1000, (2, 1 << 20)).astype(np.float32)
+    for largest in (True, False):
+        v, i = tpb.topk(torch.from_numpy(z).to(dev), 1024, -1, largest, True)
+        wv, wi = O.topk(z, 1024, -1, largest)
+        if not np.array_equal(i.cpu().numpy(), wi) or not np.array_equal(v.cpu().numpy().view(np.uint32), wv.view(np.uint32)):
+            bad.append(f"top-k k=1024 largest={largest} [2,1048576] differs")
+    torch.cuda.synchronize()
+    st = tpb._lib.device_status()
+    if st != 0:
+        bad.append(f"device status {st}")
+    flag = torch.tensor([0 if not bad else 1], dtype=torch.int32, device=dev)
+    if dist.is_initialized():
+        dist.all_reduce(flag)
+    failing = int(flag.item())
+    if failing == 0:
+        return "ok"
+    return f"FAILED on {failing} of {world} rank(s); rank {rank}: " + ("; ".join(bad[:4]) if bad else "ok here")
+
+
 def run_reference(args):
-    """--impl reference: the CPU side of the comparison, on this box's host cores.  The reference
-    has no top-k operator, so the timed code is the CPU restatement of the contract (oracle/)."""
+    """--impl reference: the CPU side of the comparison, on the host cores of the machine that runs
+    it.  The reference has no top-k operator, so the timed code is the CPU restatement of the
+    contract (oracle/)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -381,7 +517,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": len(vals), "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAME["c2"], "note": "CPU restatement of the top-k contract; the reference declares no top-k"},
+        "config": {"workload": WORKLOAD_NAME["c2"], "case": "topk k=50 [256,151936]", "l2": L2_NOTE["c2"]},
+        "method": {"timing": "wall clock per pass over the batch; CPU restatement of the top-k contract (the reference declares no top-k)"},
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": used, "kind": "port",
                          "sample": "full batch: 256 rows x 151936, rows split over host threads"},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -397,6 +534,16 @@ WORKLOAD_NAME = {
     "c3": "non-last-dim reductions of fp32 [64,4096,512] uniform(-1,1)",
     "c4": "whole-tensor reductions of 2^31 fp32, flat partitions per GPU + all-gather of packed partials",
     "c5": "top-k k=1024 both directions, fp32 [512,1048576] integers 0..999, rows split over GPUs",
+}
+
+
+# How every timed step sees cold data (the same text in both arms, so their `config` compares equal).
+L2_NOTE = {
+    "c1": "inputs rotate over 8 resident copies (512 MiB > 126 MB L2); the CPU arm's input exceeds the host caches",
+    "c2": "inputs rotate over 4 resident copies (622 MB > 126 MB L2); the CPU arm's 156 MB batch exceeds the host caches",
+    "c3": "input (512 MiB) larger than the 126 MB L2",
+    "c4": "input (8 GiB over all ranks) larger than the 126 MB L2",
+    "c5": "input (2 GiB over all ranks) larger than the 126 MB L2",
 }
 
 
@@ -426,7 +573,6 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ.pop("NCCL_DEBUG", None)   # at VERSION/WARN/INFO NCCL prints a banner on stdout; this run prints one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     tpb._lib.lib()
     peak, peak_kind = measured_peak()
@@ -466,8 +612,8 @@ def main():
         "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "strong" if strong else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAME[args.workload], "case": case.name,
-                   "l2": f"inputs rotate over {len(case.inputs)} resident copies (> 126 MB L2 in total)" if len(case.inputs) > 1 else "input larger than the 126 MB L2",
+        "config": {"workload": WORKLOAD_NAME[args.workload], "case": case.name, "l2": L2_NOTE[args.workload]},
+        "method": {"inputs_resident": len(case.inputs),
                    "timing": "one CUDA graph of K steps, CUDA events on its stream" if graphed else "K eager launches, CUDA events"},
         "rows_per_s": round(rows_total / (ms * 1e-3), 1),
         "pct_of_measured_peak": round(100 * value / world / peak, 2),
@@ -479,7 +625,7 @@ def main():
     line["roofline"] = {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                         "frac": round(per_gpu / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
-                        "kernel": {"c2": "topk_smallk_kernel", "c5": "topk_stream_kernel"}.get(args.workload, case.name),
+                        "kernel": {"c2": "topk_select_kernel", "c5": "topk_select_kernel"}.get(args.workload, case.name),
                         "algorithmic_bytes_per_launch": case.alg_bytes}
 
     # end to end (host buffers) for the headline
@@ -522,15 +668,32 @@ def main():
                              "scaling": "strong" if strong else "weak"}
         line["suite"] = suite
 
+    # the reference's own CPU reductions beside every reduction of the suite (one GPU only)
+    if world == 1 and rank == 0 and not args.no_suite:
+        try:
+            for name, ref in cpu_reference_suite(world).items():
+                for key in line["suite"]:
+                    if key == name or key.startswith(name + " ("):
+                        line["suite"][key]["cpu_reference"] = ref
+        except Exception as e:
+            line["cpu_reference_error"] = str(e)[:200]
+
+    # untimed correctness evidence at this number of ranks
+    try:
+        line["parity"] = parity_check(torch, tpb, dev, rank, world)
+    except Exception as e:
+        line["parity"] = f"FAILED: {type(e).__name__}: {str(e)[:200]}"
     try:
         line["device_status"] = tpb._lib.device_status()
     except Exception:
         pass
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    # the one JSON line comes last, after the process group (and whatever NCCL prints) is gone
+    if rank == 0:
+        sys.stdout.flush()
+        print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

@@ -117,7 +117,12 @@ size_t tpb200_reduce_workspace_bytes(int op, int dtype, int ndim, const int64_t*
  * out_val / out_idx are written contiguously as [non-selected dims in their original order..., k]:
  * for dim = last that is the input's shape with dim replaced by k; for another dim the caller
  * reports the result as a permuted view.  The non-selected dims must collapse to at most two
- * strided dims; k <= 2048, or any k on rows of at most 16384 elements.
+ * strided dims; k <= 2048, or any k on rows of at most 16384 elements; rows * slices per row must
+ * stay below 2^31 (rows ride on grid.x).
+ * Long rows (32 K elements and more) go through a kernel that fixes its threshold from a sample of
+ * the row and verifies it afterwards; rows that fail the check (sorted rows, rows of equal values,
+ * rows with fewer than k numbers) are redone by a second launch that needs no assumption.  The
+ * result is exact either way; only the time depends on the data.
  */
 int tpb200_topk(const void* in, int dtype, int ndim, const int64_t* sizes, const int64_t* strides,
                 int dim, int64_t k, int largest, int sorted, void* out_val, int64_t* out_idx,
@@ -125,6 +130,19 @@ int tpb200_topk(const void* in, int dtype, int ndim, const int64_t* sizes, const
 
 size_t tpb200_topk_workspace_bytes(int dtype, int ndim, const int64_t* sizes, const int64_t* strides,
                                    int dim, int64_t k);
+
+/* What the planner chose for a top-k call (no launch, no GPU needed); for benchmarks and tests.
+ * No reference counterpart.  info[0..n_info) receives, in this order:
+ *   0 scanning kernel (0 none, 1 whole-row sort, 2 rendezvous kernel, 3 ring kernel)
+ *   1 its slices per row            2 its warps per CTA
+ *   3 1 if the sampled-threshold kernel runs first    4 its CTAs per row (cluster size)
+ *   5 its warps per CTA             6 rank of the threshold key in the sample
+ *   7 candidate words per row       8 sample tiles per warp
+ *   9 kernel launches of one call   10 workspace bytes
+ */
+#define TPB200_PLAN_INFO_FIELDS 11
+int tpb200_topk_plan_info(int dtype, int ndim, const int64_t* sizes, const int64_t* strides, int dim,
+                          int64_t k, int64_t* info, int n_info);
 
 /* ---- sharded whole-tensor reductions: per-GPU partial, then a rank-ordered combine ------------
  * No reference counterpart (the reference is single-GPU: p10/src/backend/cuda/CUDAAllocator.cpp:87-88).
@@ -161,10 +179,15 @@ int tpb200_reduce_combine(int op, const void* partials, int n_parts, int64_t tot
  *                 tpb200_exchange_buffer_bytes() bytes and is zero-filled once before the first call
  *   n / global_offset / total_count   this rank's flat partition and the size of the whole tensor
  * All ranks must issue the same sequence of calls (one process per GPU, one kernel in flight per
- * rank).  A rank whose peers never arrive gives up after a bounded wait: nothing is written and
- * tpb200_device_status() reports it.  world <= 16.
+ * rank).  A rank whose peers do not arrive gives up after a bounded wait (about half a second by
+ * default; launch skew between ranks must stay below it): its outputs are set to NaN / -1, so that the
+ * previous call's answer cannot pass for this one's, and tpb200_device_status() reports 5.  The caller
+ * reads the status wherever it synchronises anyway.  world <= 16.
+ * tpb200_set_exchange_wait_polls sets the bound for the calls that follow, in polls of at least
+ * 100 ns each (1 .. 2^25, a few seconds; default 2^22).
  */
 size_t tpb200_exchange_buffer_bytes(void);
+int tpb200_set_exchange_wait_polls(int polls);
 int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, int64_t n, int64_t global_offset,
                                  int64_t total_count, int64_t correction, int rank, int world,
                                  void* const* peer_buffers, void* out_val, int64_t* out_idx,
@@ -204,9 +227,12 @@ int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int64_t n, int6
                               void* out_val, int64_t* out_idx, void* stream);
 
 /* ---- diagnostics ------------------------------------------------------------------------------
- * Every device-side wait in these kernels (on a bulk copy into shared memory) is bounded; a kernel
- * whose wait gave up leaves its outputs unwritten and sets a per-device status word.  This call
- * SYNCHRONISES with the device, returns the word in *status_out (0 = no wait ever gave up) and
+ * Every device-side wait in these kernels is bounded: the ring and rendezvous waits between the
+ * warps of a top-k CTA, and the wait of the fused exchange for the records of the other ranks.  A
+ * kernel whose wait gave up sets a per-device status word; a top-k kernel then leaves its outputs
+ * unwritten, the fused exchange writes NaN / -1 so that a timed-out call cannot pass for a result.
+ * Status values: 0 no wait ever gave up; 1..4, 6..8 a top-k wait (which one is in the low byte);
+ * 5 the peer exchange.  This call SYNCHRONISES with the device, returns the word in *status_out and
  * clears it.  No reference counterpart.
  */
 int tpb200_device_status(int* status_out);

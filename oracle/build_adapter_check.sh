@@ -6,10 +6,10 @@
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 ROOT="$(dirname "$HERE")"
-REF="${TP_REFERENCE_ROOT:-/root/reference}"
+REF="${TP_REFERENCE_ROOT:-}"
 OUT="$HERE/_ref"
 CUDA="${CUDA_HOME:-/usr/local/cuda}"
-if [ ! -f "$REF/p10/src/backend/cuda/CUDAAllocator.cpp" ] || [ ! -d "$OUT/obj" ]; then
+if [ -z "$REF" ] || [ ! -f "$REF/p10/src/backend/cuda/CUDAAllocator.cpp" ] || [ ! -d "$OUT/obj" ]; then
     echo "build_adapter_check: reference checkout or oracle/_ref/obj missing; skipping" >&2
     exit 0
 fi
@@ -22,6 +22,6 @@ $CXX -c "$ROOT/tensorplay_b200/csrc/adapter/tensorplay_adapter.cpp" -o "$OUT/obj
 $CXX -c "$ROOT/tests/adapter_check.cpp" -o "$OUT/obj_cuda/adapter_check.o"
 OBJS=$(ls "$OUT"/obj/*.o | grep -v '/Allocator.o$')
 g++ -o "$OUT/adapter_check" "$OUT"/obj_cuda/*.o $OBJS -fopenmp \
-    -L"$ROOT/tensorplay_b200" -ltpb200 -L"$CUDA/lib64" -lcudart \
-    -Wl,-rpath,'$ORIGIN/../../tensorplay_b200' -Wl,-rpath,"$CUDA/lib64"
+    -L"$ROOT/tensorplay_b200" -ltpb200 -L"$HERE" -ltporacle -L"$CUDA/lib64" -lcudart \
+    -Wl,-rpath,'$ORIGIN/../../tensorplay_b200' -Wl,-rpath,'$ORIGIN/..' -Wl,-rpath,"$CUDA/lib64"
 echo "build_adapter_check: built $OUT/adapter_check"

@@ -7,27 +7,37 @@
 # What it runs:
 #   1. the reference's generator  tools/codegen/gen.py  on its two yaml files -- the CPU kernels
 #      call generated Tensor methods (Tensor::mean, operator-, ...), so TensorGenerated.{h,cpp}
-#      is needed; only PyYAML is required;
+#      is needed; only PyYAML is required.  The schema gets one additive entry (top-k, which the
+#      reference does not declare: tensorplay_b200/csrc/adapter/topk_schema.yaml), so that the
+#      generated Tensor class has the topk method the adapter check calls;
 #   2. g++ with the reference's own flags (CMakeLists.txt:213,470: -O3 -march=native, OpenMP on,
 #      no USE_CUDA / USE_ONEDNN / USE_MKL) on the P10 core and CPU kernel files;
 #   3. a link with oracle/ref_driver.cpp.
-# The reference's CMake build is not run.  Skips quietly (exit 0) when no checkout is present.
+# The reference's CMake build is not run.  TP_REFERENCE_ROOT names the checkout; without it the
+# script skips quietly (exit 0) and whatever was built before stays in place.
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${TP_REFERENCE_ROOT:-/root/reference}"
+REF="${TP_REFERENCE_ROOT:-}"
 OUT="$HERE/_ref"
-if [ ! -f "$REF/p10/src/backend/cpu/ReductionKernels.cpp" ]; then
-    echo "build_ref: no TensorPlay checkout at $REF; skipping" >&2
+SCHEMA_ADD="$HERE/../tensorplay_b200/csrc/adapter/topk_schema.yaml"
+if [ -z "$REF" ] || [ ! -f "$REF/p10/src/backend/cpu/ReductionKernels.cpp" ]; then
+    echo "build_ref: TP_REFERENCE_ROOT does not name a TensorPlay checkout; skipping" >&2
     exit 0
 fi
-if [ -f "$OUT/libtpref.so" ] && [ "$OUT/libtpref.so" -nt "$HERE/ref_driver.cpp" ] && [ "${1:-}" != "--force" ]; then
+if [ -f "$OUT/libtpref.so" ] && [ "$OUT/libtpref.so" -nt "$HERE/ref_driver.cpp" ] && [ "$OUT/libtpref.so" -nt "$SCHEMA_ADD" ] && [ "${1:-}" != "--force" ]; then
     echo "build_ref: $OUT/libtpref.so is up to date"
     exit 0
 fi
-mkdir -p "$OUT/gen/tensorplay/ops" "$OUT/pkg" "$OUT/obj"
-python3 "$REF/tools/codegen/gen.py" --yaml "$REF/config/native_functions.yaml" \
+mkdir -p "$OUT/gen/tensorplay/ops" "$OUT/obj"
+PKG_SCRATCH="$(mktemp -d)"       # the generator also writes Python stubs; they are not needed
+trap 'rm -rf "$PKG_SCRATCH"' EXIT
+# the reference's schema plus the one additive entry for top-k (the reference declares none)
+cat "$REF/config/native_functions.yaml" > "$OUT/native_functions_plus_topk.yaml"
+printf '\n' >> "$OUT/native_functions_plus_topk.yaml"
+grep -v '^#' "$SCHEMA_ADD" >> "$OUT/native_functions_plus_topk.yaml"
+python3 "$REF/tools/codegen/gen.py" --yaml "$OUT/native_functions_plus_topk.yaml" \
     --derivatives "$REF/config/derivatives.yaml" --out_dir "$OUT/gen/tensorplay/ops" \
-    --pkg_out "$OUT/pkg" > "$OUT/gen.log" 2>&1
+    --pkg_out "$PKG_SCRATCH" > "$OUT/gen.log" 2>&1
 
 CXXFLAGS="-std=c++20 -O3 -march=native -fopenmp -w -fPIC -I$REF/p10/include -I$OUT/gen"
 SRCS=()

@@ -34,13 +34,24 @@ _lib = None
 _ref = None
 
 
+def reference_env() -> dict:
+    """Environment for the build scripts: TP_REFERENCE_ROOT names the TensorPlay checkout; when it is
+    not set, a checkout in a directory `reference` beside this repository is used if there is one."""
+    env = dict(os.environ)
+    if not env.get("TP_REFERENCE_ROOT"):
+        sibling = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+        if os.path.isfile(os.path.join(sibling, "p10", "src", "backend", "cpu", "ReductionKernels.cpp")):
+            env["TP_REFERENCE_ROOT"] = sibling
+    return env
+
+
 def build(force: bool = False) -> None:
     """Compile libtporacle.so (and the reference path when its sources are present)."""
     so = os.path.join(_HERE, "libtporacle.so")
     src = os.path.join(_HERE, "tp_oracle.c")
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
         subprocess.check_call(["make", "-C", _HERE, "-B", "libtporacle.so"], stdout=subprocess.DEVNULL)
-    subprocess.check_call(["bash", os.path.join(_HERE, "build_ref.sh")], stdout=subprocess.DEVNULL)
+    subprocess.check_call(["bash", os.path.join(_HERE, "build_ref.sh")], stdout=subprocess.DEVNULL, env=reference_env())
 
 
 def lib() -> ctypes.CDLL:

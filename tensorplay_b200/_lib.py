@@ -26,7 +26,7 @@ SYMBOLS = [
     "tpb200_topk", "tpb200_topk_workspace_bytes", "tpb200_reduce_partial",
     "tpb200_reduce_partial_workspace_bytes", "tpb200_reduce_combine", "tpb200_topk_merge",
     "tpb200_device_status", "tpb200_reduce_all_noalloc", "tpb200_exchange_buffer_bytes",
-    "tpb200_reduce_fused_exchange",
+    "tpb200_reduce_fused_exchange", "tpb200_topk_plan_info", "tpb200_set_exchange_wait_polls",
 ]
 
 _I64P = ctypes.POINTER(ctypes.c_int64)
@@ -77,6 +77,10 @@ def lib() -> ctypes.CDLL:
     L.tpb200_exchange_buffer_bytes.argtypes = []
     L.tpb200_reduce_fused_exchange.restype = i
     L.tpb200_reduce_fused_exchange.argtypes = [i, vp, i, i64, i64, i64, i64, i, i, ctypes.POINTER(ctypes.c_void_p), vp, vp, vp, sz, vp]
+    L.tpb200_set_exchange_wait_polls.restype = i
+    L.tpb200_set_exchange_wait_polls.argtypes = [i]
+    L.tpb200_topk_plan_info.restype = i
+    L.tpb200_topk_plan_info.argtypes = [i, i, _I64P, _I64P, i, i64, _I64P, i]
     L.tpb200_device_status.restype = i
     L.tpb200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     _lib = L
@@ -97,6 +101,18 @@ def check(rc: int) -> None:
     if rc == ERR_UNSUPPORTED:
         raise NotImplementedError(msg)
     raise Tpb200Error(rc, msg)
+
+
+PLAN_FIELDS = ("scan_kernel", "scan_slices", "scan_warps", "select", "select_ctas_per_row", "select_warps",
+               "select_rank", "select_cap", "select_sample_tiles", "launches", "workspace_bytes")
+
+
+def topk_plan_info(sizes, strides, dim: int, k: int) -> dict:
+    """The planner's choice for a top-k call on a float32 tensor of these sizes / strides."""
+    info = (ctypes.c_int64 * len(PLAN_FIELDS))()
+    check(lib().tpb200_topk_plan_info(F32, len(sizes), i64_array(list(sizes)), i64_array(list(strides)), dim, k,
+                                      info, len(PLAN_FIELDS)))
+    return dict(zip(PLAN_FIELDS, [int(v) for v in info]))
 
 
 def device_status() -> int:

@@ -11,10 +11,12 @@
 #include "Dispatcher.h"
 #include "Exception.h"
 
+#include <algorithm>
 #include <cstdint>
 #include <limits>
 #include <optional>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "../../../include/tpb200.h"
@@ -33,6 +35,7 @@ struct Previous {
     void* var = nullptr; void* var_dim = nullptr; void* std_ = nullptr; void* std_dim = nullptr;
     void* prod = nullptr; void* prod_dim = nullptr; void* norm = nullptr; void* norm_dim = nullptr;
     void* all = nullptr; void* all_dim = nullptr; void* any = nullptr; void* any_dim = nullptr;
+    void* topk = nullptr;
 } g_prev;
 
 void* lookup(const char* name) {
@@ -84,7 +87,9 @@ Tensor run(int op, const Tensor& self, uint64_t mask, int index_dim, int64_t cor
     return out;
 }
 
-bool ours(const Tensor& self) { return self.dtype() == DType::Float32; }
+// float32 tensors of at most TPB200_MAX_DIMS dims run here; everything else goes to the kernel that
+// was registered before (TPB200_ERR_UNSUPPORTED exists for exactly that)
+bool ours(const Tensor& self) { return self.dtype() == DType::Float32 && self.dim() <= TPB200_MAX_DIMS; }
 bool same_dtype(DType d) { return d == DType::Undefined || d == DType::Float32; }
 
 template <class Fn, class... A>
@@ -216,6 +221,50 @@ Tensor tpb_any_dim(const Tensor& self, const IntList& dim, bool keepdim) {
     return run(TPB200_OP_ANY, self, m, -1, 1, shape);
 }
 
+// topk(Tensor self, int64_t k, int64_t dim=-1, bool largest=true, bool sorted=true) -> (values, indices):
+// a new operator (schema entry: topk_schema.yaml beside this file; the generated Tensor::topk
+// reaches this function as DispatchStub<std::tuple<Tensor, Tensor>, const Tensor&, int64_t, int64_t,
+// bool, bool>).  The kernels write [other dims..., k]; for dim != last the result is handed back as
+// the permuted view that puts k where `dim` was.
+std::tuple<Tensor, Tensor> tpb_topk(const Tensor& self, int64_t k, int64_t dim, bool largest, bool sorted) {
+    using Fn = std::tuple<Tensor, Tensor> (*)(const Tensor&, int64_t, int64_t, bool, bool);
+    if (!ours(self) || self.dim() > TPB200_MAX_DIMS) {
+        if (!g_prev.topk) TP_THROW(NotImplementedError, "topk not implemented for this dtype on CUDA");
+        return reinterpret_cast<Fn>(g_prev.topk)(self, k, dim, largest, sorted);
+    }
+    const int nd = (int)self.dim();
+    int64_t d = dim < 0 ? dim + std::max(nd, 1) : dim;
+    if (d < 0 || d >= std::max(nd, 1)) TP_THROW(RuntimeError, "Dimension out of range");
+    const IntList sizes = static_cast<IntList>(self.shape());
+    const IntList strides = self.strides();
+    if (k < 0 || k > (nd ? sizes[d] : 1)) TP_THROW(RuntimeError, "selected index k out of range");
+    IntList inner;                                   // [other dims in their order..., k]
+    for (int i = 0; i < nd; ++i) if (i != d) inner.push_back(sizes[i]);
+    inner.push_back(k);
+    Tensor values(inner, DType::Float32, self.device());
+    Tensor indices(inner, DType::Int64, self.device());
+    const size_t ws_bytes = tpb200_topk_workspace_bytes(TPB200_F32, nd, sizes.data(), strides.data(), (int)d, k);
+    Tensor ws;
+    if (ws_bytes) ws = Tensor(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    const int rc = tpb200_topk(self.data_ptr(), TPB200_F32, nd, sizes.data(), strides.data(), (int)d, k, largest ? 1 : 0,
+                               sorted ? 1 : 0, values.data_ptr(), indices.data_ptr<int64_t>(),
+                               ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, nullptr);
+    if (rc == TPB200_ERR_UNSUPPORTED && g_prev.topk) return reinterpret_cast<Fn>(g_prev.topk)(self, k, dim, largest, sorted);
+    if (rc != TPB200_OK) raise_last();
+    if (nd == 0 || d == nd - 1) return {values, indices};
+    // view with k moved from the last position back to `dim`
+    IntList shape, vstrides;
+    IntList cs(inner.size());
+    int64_t acc = 1;
+    for (int i = (int)inner.size() - 1; i >= 0; --i) { cs[i] = acc; acc *= inner[i]; }
+    for (int i = 0, j = 0; i < nd; ++i) {
+        if (i == d) { shape.push_back(k); vstrides.push_back(cs[nd - 1]); }
+        else { shape.push_back(inner[j]); vstrides.push_back(cs[j]); ++j; }
+    }
+    return {Tensor(values.impl()->storage(), shape, vstrides, DType::Float32, 0),
+            Tensor(indices.impl()->storage(), shape, vstrides, DType::Int64, 0)};
+}
+
 }  // namespace
 
 namespace tensorplay {
@@ -232,6 +281,7 @@ TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
     g_prev.norm = lookup("norm");       g_prev.norm_dim = lookup("norm.dim");
     g_prev.all = lookup("all");         g_prev.all_dim = lookup("all.dim");
     g_prev.any = lookup("any");         g_prev.any_dim = lookup("any.dim");
+    g_prev.topk = lookup("topk");
     m.impl("sum", tpb_sum);             m.impl("sum.dim_IntList", tpb_sum_dim);
     m.impl("mean", tpb_mean);           m.impl("mean.dim", tpb_mean_dim);
     m.impl("max", tpb_max);             m.impl("max.dim", tpb_max_dim);
@@ -243,6 +293,7 @@ TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
     m.impl("norm", tpb_norm);           m.impl("norm.dim", tpb_norm_dim);
     m.impl("all", tpb_all);             m.impl("all.dim", tpb_all_dim);
     m.impl("any", tpb_any);             m.impl("any.dim", tpb_any_dim);
+    m.impl("topk", tpb_topk);
 }
 
 }  // namespace tensorplay

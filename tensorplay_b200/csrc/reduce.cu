@@ -23,6 +23,7 @@
 #include "host_util.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <mutex>
 #include <string>
@@ -850,11 +851,17 @@ extern "C" int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int6
 //                                ahead of another: it needs the other's flag of its own epoch)
 //   unsigned flags[kMaxPeers]    flags[j] = last epoch whose record rank j has delivered here
 //   unsigned epoch, ticket       local call counter (ticket is unused padding)
-// Every wait is bounded; on give-up nothing is written and the status word gets kErrExchange.
+// Every wait is bounded (tpb200_set_exchange_wait_polls; about half a second by default): a rank
+// whose peers do not arrive in that time writes NaN / -1 to its outputs -- a timed-out call must not
+// pass for a result: the output buffers may still hold the previous call's answer -- and sets the
+// status word to kErrExchange.
 namespace tpb {
 
 constexpr int kMaxPeers = 16;
 constexpr int kErrExchange = 5;
+constexpr int kExchangePollsDefault = 1 << 22;   // polls of 100 ns and more each
+constexpr int kExchangePollsMax = 1 << 25;       // a few seconds
+static std::atomic<int> g_exchange_polls{kExchangePollsDefault};
 
 struct ExchangeBuf {
     Packed slots[2][kMaxPeers];
@@ -878,7 +885,8 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 template <class Acc>
 __global__ void __launch_bounds__(32)
 finalize_exchange_kernel(const Packed* __restrict__ ws, int S, long long idx_offset, int rank, int world,
-                         PeerPtrs peers, double total_count, Epilogue e, float* ov, long long* oi, int* status) {
+                         PeerPtrs peers, double total_count, Epilogue e, float* ov, long long* oi, int* status,
+                         int max_polls) {
     const int lane = threadIdx.x & 31;
     ExchangeBuf* mine = peers.p[rank];
     Acc r;
@@ -905,13 +913,15 @@ finalize_exchange_kernel(const Packed* __restrict__ ws, int S, long long idx_off
         for (int j = 0; j < world && ok; ++j) {
             int spin = 0;
             while ((int)(ld_acquire_sys(&mine->flags[j]) - ep) < 0) {
-                if (++spin > (1 << 22)) { ok = false; break; }
+                if (++spin > max_polls) { ok = false; break; }
                 __nanosleep(100);
             }
         }
         mine->epoch = ep;
         if (!ok) {
             if (status) atomicMax(status, kErrExchange);
+            if (ov) ov[0] = NAN;
+            if (oi) oi[0] = -1;
         } else {
             // the same rank-ordered merge on every GPU
             Acc all;
@@ -930,6 +940,13 @@ finalize_exchange_kernel(const Packed* __restrict__ ws, int S, long long idx_off
 }  // namespace tpb
 
 extern "C" size_t tpb200_exchange_buffer_bytes(void) { return sizeof(tpb::ExchangeBuf); }
+
+extern "C" int tpb200_set_exchange_wait_polls(int polls) {
+    if (polls < 1 || polls > tpb::kExchangePollsMax)
+        return fail(TPB200_ERR_INVALID, "the exchange wait takes 1..%d polls, %d given", tpb::kExchangePollsMax, polls);
+    tpb::g_exchange_polls.store(polls, std::memory_order_relaxed);
+    return TPB200_OK;
+}
 
 extern "C" int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, int64_t n, int64_t global_offset,
                                             int64_t total_count, int64_t correction, int rank, int world,
@@ -964,14 +981,13 @@ extern "C" int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, i
     const float* x = (const float*)in;
     int* status = device_status_word();
     const double tc = (double)total_count;
-    RowGeom& g = pl.row;
-    (void)g;
+    const int max_polls = g_exchange_polls.load(std::memory_order_relaxed);
 #define TPB_LAUNCH_X(ACC)                                                                                    \
     do {                                                                                                     \
         row_split_kernel<ACC><<<dim3((unsigned)pl.S, 1), pl.threads, 0, st>>>(x, pl.row, pl.chunk, (Packed*)workspace); \
         TPB_LAUNCH_OK("row_split_kernel");                                                                   \
         finalize_exchange_kernel<ACC><<<1, 32, 0, st>>>((const Packed*)workspace, pl.S, (long long)global_offset, \
-            rank, world, peers, tc, e, ov, oi, status);                                                      \
+            rank, world, peers, tc, e, ov, oi, status, max_polls);                                           \
     } while (0)
     switch (fam) {
         case FAM_SUM: TPB_LAUNCH_X(SumAcc); break;

@@ -170,6 +170,7 @@ __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom
 // kernel may have started before the first one finished: wait for it (a no-op otherwise).
 __device__ __forceinline__ bool row_wanted(const int* redo, long long r) {
     if (redo == nullptr) return true;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     return *(const volatile int*)(redo + r) != 0;
 }
@@ -1062,6 +1063,8 @@ topk_merge_pairs_kernel(const float* __restrict__ cv, const long long* __restric
     }
 }
 
+__device__ __forceinline__ int pow2_ceil_dev(int v) { return v <= 1 ? 1 : 1 << (32 - __clz(v - 1)); }
+
 }  // namespace tpb
 
 #include "topk_select.cuh"
@@ -1099,42 +1102,59 @@ static int poisson_rank(double mu, double eps) {
 
 // Does the sampled-threshold kernel apply, and with which geometry?  (k, row length, rows only:
 // the values are never looked at on the host.)
+//   candidate buffer   6 k words (4096 .. 8192): the expected number of candidates is 2 to 3 k, and on
+//                      tie-heavy rows whole classes of equal values are candidates together
+//   CTA width          16 warps wherever a slice holds six rounds of tiles for them.  Measured on
+//                      [512, 2^20], k = 1024: 512 CTAs of 16 warps in two waves 358 us, 512 CTAs of
+//                      8 warps in one wave 444 us (an SM moves 46 GB/s with two 16-warp CTAs and 38 GB/s
+//                      with three or four 8-warp CTAs); [256, 151936], k = 50: 32.1 against 38.6 us
+//   CTAs per row       1, 2, 4 or 8 (a cluster), as many as one wave of CTAs on the GPU holds
+//   sample             1, 2 or 4 tiles per warp: the smallest sample whose threshold is expected to let
+//                      at most 40 % of the buffer through
 static bool plan_select(long long rows, long long len, long long k, int sms, TopkPlan* pl) {
     int on = 1;
     if (env_int("TPB200_TOPK_SELECT", &on) && on == 0) return false;
     if (k < 1 || k > kMaxStreamK || len < 32 * 1024 || rows > 0x3fffffffLL / kSelMaxCluster) return false;
     const long long tiles = len / kWarpTile;
-    // candidate buffer: 8 k words, at most 8192 (12 bytes of shared memory per word with cut's
-    // partition target); the CTA width must leave the SM full with that much shared memory per CTA
-    const int cap = (int)std::min<long long>(8192, std::max<long long>(1024, pow2_ceil(8 * k)));
-    int nw = len >= 256 * 1024 ? 16 : (len >= 64 * 1024 ? 8 : 4);
-    if (cap > 2048 && nw < 8) nw = 8;
-    if (cap > 4096) nw = 16;
+    const int cap = (int)std::min<long long>(8192, std::max<long long>(4096, round_up(6 * k, 256)));
+    const size_t smem = (size_t)cap * 8 + 4096;     // per CTA, with the static part
+    auto per_sm = [&](int nw) {
+        const int by_threads = nw == 4 ? 7 : (nw == 8 ? 4 : 2);
+        return (int)std::min<long long>(by_threads, (long long)(227 * 1024) / (long long)smem);
+    };
+    int nw = tiles >= 6LL * 16 ? 16 : (tiles >= 6LL * 8 ? 8 : 4);
     int fw = 0;
     if (env_int("TPB200_SEL_WARPS", &fw) && (fw == 4 || fw == 8 || fw == 16)) nw = fw;
-    const int per_sm = nw == 4 ? 7 : (nw == 8 ? 4 : 2);
-    // slices per row: the largest cluster that still fits the CTA slots of the GPU once, with at
-    // least eight rounds of tiles per slice
+    if (per_sm(nw) < 1) return false;
+    const long long slots = (long long)sms * per_sm(nw);
     int S = 1;
-    while (S < kSelMaxCluster && rows * (2LL * S) <= (long long)sms * per_sm && tiles / (2LL * S) >= 8LL * nw) S *= 2;
+    while (S < kSelMaxCluster && rows * (2LL * S) <= slots && tiles / (2LL * S) >= 6LL * nw) S *= 2;
     int fs = 0;
     if (env_int("TPB200_SEL_SLICES", &fs) && (fs == 1 || fs == 2 || fs == 4 || fs == 8)) S = fs;
-    if (tiles / S < 2LL * nw) return false;
-    const double m = (double)S * nw * kWarpTile;          // sampled elements
-    const double mu = (double)k * m / (double)len;         // of which among the k best, on average
-    int r = poisson_rank(mu, 1e-7);
-    int fr = 0;
-    if (env_int("TPB200_SEL_RANK", &fr) && fr >= 1) r = fr;
-    if (r > std::min(96 * S, 384)) return false;
-    const double expect = (double)r * (double)len / m;     // candidates per row, values all distinct
-    if (expect * 1.5 > (double)cap) return false;
+    const long long slice_tiles = tiles / S;
+    int fr = 0, ft = 0;
+    const bool forced_rank = env_int("TPB200_SEL_RANK", &fr) && fr >= 1;
+    const bool forced_tpw = env_int("TPB200_SEL_TPW", &ft) && (ft == 1 || ft == 2 || ft == 4);
+    int tpw = 0, r = 0;
+    for (int t : {1, 2, 4}) {
+        if (forced_tpw && t != ft) continue;
+        if ((long long)(t + 1) * nw * 3 > slice_tiles) break;        // sample at most a third of the slice
+        const double m = (double)t * nw * kWarpTile;                // sampled elements per CTA
+        const double mu = (double)k * m / (double)len;               // of which among the row's k best, on average
+        const int rr = forced_rank ? fr : poisson_rank(mu, 1e-7);
+        if (rr > 96) continue;
+        const double expect = (double)rr * (double)len / m;          // candidates per row, values all distinct
+        tpw = t;
+        r = rr;
+        if (expect <= 0.4 * cap) break;
+    }
+    if (tpw == 0) return false;
+    if (!forced_rank && (double)r * (double)len / ((double)tpw * nw * kWarpTile) > 0.7 * cap) return false;
     SelGeom& sg = pl->sel;
     sg.S = S;
     sg.r = r;
     sg.cap = cap;
-    sg.prefetch = 2;
-    env_int("TPB200_SEL_PREFETCH", &sg.prefetch);
-    sg.prefetch = std::max(0, std::min(8, sg.prefetch));
+    sg.tpw = tpw;
     sg.trigger = 1;
     sg.chunk = round_up(ceil_div(len, S), 4);
     pl->sel_warps = nw;
@@ -1332,7 +1352,7 @@ static int select_launch(const TopkPlan& pl, const float* in, float* ov, long lo
     const TopkGeom& g = pl.g;
     SelGeom sg = pl.sel;
     sg.trigger = dependent_launch_on() ? 1 : 0;
-    const size_t sm = (size_t)sg.cap * 12;
+    const size_t sm = (size_t)sg.cap * 8;
     const unsigned grid = (unsigned)(g.rows * sg.S);
     const int nw = pl.sel_warps;
     cudaError_t e = cudaSuccess;
@@ -1340,7 +1360,7 @@ static int select_launch(const TopkPlan& pl, const float* in, float* ov, long lo
     do {                                                                                                  \
         int rc = allow_smem(topk_select_kernel<LARGEST, V, W>, sm);                                       \
         if (rc) return rc;                                                                                \
-        e = launch_ex(topk_select_kernel<LARGEST, V, W>, grid, W * 32, sm, st, sg.S, false, in, g, sg, ov, oi, redo); \
+        e = launch_ex(topk_select_kernel<LARGEST, V, W>, grid, W * 32, sm, st, sg.S, sg.trigger != 0, in, g, sg, ov, oi, redo); \
     } while (0)
     if (pl.vec) { if (nw == 16) TPB_LAUNCH_SELECT(true, 16); else if (nw == 8) TPB_LAUNCH_SELECT(true, 8); else TPB_LAUNCH_SELECT(true, 4); }
     else        { if (nw == 16) TPB_LAUNCH_SELECT(false, 16); else if (nw == 8) TPB_LAUNCH_SELECT(false, 8); else TPB_LAUNCH_SELECT(false, 4); }
@@ -1405,8 +1425,9 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
         int rc = allow_smem(topk_sort_kernel<LARGEST, false>, msm);
         if (rc) return rc;
         int mthreads = std::min(kSortThreads, std::max(32, pl.mergeN / 2));
-        topk_sort_kernel<LARGEST, false><<<(unsigned)g.rows, mthreads, msm, st>>>(in, g, w, g.S * (int)g.k, pl.mergeN, ov, oi, (const int*)redo);
-        TPB_LAUNCH_OK("topk_sort_kernel(merge)");
+        e = launch_ex(topk_sort_kernel<LARGEST, false>, (unsigned)g.rows, mthreads, msm, st, 1, dep, in, g, (const unsigned long long*)w,
+                      g.S * (int)g.k, pl.mergeN, ov, oi, (const int*)redo);
+        if (e != cudaSuccess) return cuda_fail(e, "topk_sort_kernel(merge)");
     }
     return TPB200_OK;
 }
@@ -1421,6 +1442,33 @@ extern "C" size_t tpb200_topk_workspace_bytes(int dtype, int ndim, const int64_t
     TopkPlan pl;
     if (topk_plan((const void*)16, ndim, sizes, strides, dim, k, &pl) != TPB200_OK) return 0;
     return pl.ws_bytes;
+}
+
+#ifdef TPB200_TRACE
+extern "C" int tpb200_debug_trace(long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, tpb::g_sel_trace, sizeof(long long) * n);
+}
+extern "C" int tpb200_debug_trace_clear(void) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, tpb::g_sel_trace) != cudaSuccess) return 1;
+    return (int)cudaMemset(p, 0, sizeof(tpb::g_sel_trace));
+}
+#endif
+
+extern "C" int tpb200_topk_plan_info(int dtype, int ndim, const int64_t* sizes, const int64_t* strides,
+                                     int dim, int64_t k, int64_t* info, int n_info) {
+    if (dtype != TPB200_F32) return fail(TPB200_ERR_UNSUPPORTED, "only float32 input is supported (dtype code %d)", dtype);
+    if (!info || n_info < 1) return fail(TPB200_ERR_INVALID, "info is NULL or empty");
+    TopkPlan pl;
+    int rc = topk_plan((const void*)16, ndim, sizes, strides, dim, k, &pl);
+    if (rc) return rc;
+    const int scan_launches = pl.path == TK_NONE ? 0 : 1 + (pl.path != TK_SORTROW && pl.g.S > 1 ? 1 : 0);
+    const int64_t v[TPB200_PLAN_INFO_FIELDS] = {
+        (int64_t)pl.path, pl.g.S, pl.g.warps, pl.select ? 1 : 0, pl.select ? pl.sel.S : 0,
+        pl.select ? pl.sel_warps : 0, pl.select ? pl.sel.r : 0, pl.select ? pl.sel.cap : 0, pl.select ? pl.sel.tpw : 0,
+        scan_launches + (pl.select ? 1 : 0), (int64_t)pl.ws_bytes};
+    for (int i = 0; i < n_info && i < TPB200_PLAN_INFO_FIELDS; ++i) info[i] = v[i];
+    return TPB200_OK;
 }
 
 extern "C" int tpb200_topk(const void* in, int dtype, int ndim, const int64_t* sizes,

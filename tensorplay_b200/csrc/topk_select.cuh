@@ -1,38 +1,47 @@
 // One-pass top-k with a sampled threshold, for long rows: topk_select_kernel.
-// Included by topk.cu after the rank-word, sort and cut helpers.
+// Included by topk.cu after the rank-word and sort helpers.
 //
-// The two streaming kernels of topk.cu learn their threshold while they scan: it only rises when a
+// The two scanning kernels of topk.cu learn their threshold while they scan: it only rises when a
 // cut has seen k candidates, so a row cannot be split over CTAs without every slice paying for its
 // own k candidates, and the first part of every row is scanned with a weak threshold (k(1 + ln(n/k))
 // candidates per row at best).  This kernel fixes the threshold BEFORE the scan, from a sample, and
 // verifies it afterwards (the scheme of Floyd and Rivest's SELECT: sample, pick a pivot with a safety
 // margin, partition, check):
 //
-//   1. sample     every warp of the S CTAs of a row loads its first 1024-element tile and sorts its
-//                 32 lane maxima; the CTA's best 128 are exchanged over distributed shared memory
-//                 (the S CTAs of a row are one thread-block cluster) and every CTA finds the r-th
-//                 largest key of the union.  r is chosen on the host so that, for a row whose order
-//                 carries no information about its values, fewer than k elements reach that key with
+//   1. sample     every warp of a CTA streams its first `tpw` 1024-element tiles of the CTA's slice
+//                 and keeps one maximum per lane; the CTA's threshold key is the r-th largest of its
+//                 lane maxima.  r is chosen on the host so that, for a row whose order carries no
+//                 information about its values, fewer than k elements of the ROW reach that key with
 //                 probability below 1e-7: the number of sampled elements among the row's k best is
 //                 Poisson(mu), mu = k * sample / n, and r is the smallest rank with
-//                 P(Poisson(mu) >= r) <= 1e-7.
+//                 P(Poisson(mu) >= r) <= 1e-7.  (A lane maximum ranks at or below the element of the
+//                 same rank, so the estimate errs towards more candidates.)  The loads of the first
+//                 scan tile are already in flight while the threshold is worked out.
 //   2. scan       one pass, no barrier, no cut: an element is a candidate iff its key reaches the
 //                 threshold key (one float compare; ties of the threshold value are all taken, so the
 //                 index order among them is decided later and exactly).  Candidates are rank words in
-//                 the CTA's shared memory, one atomic each.
-//   3. merge      cluster barrier; the CTAs copy their candidates into the buffer of the cluster's
-//                 first CTA through distributed shared memory (plain remote stores); that CTA cuts
-//                 them to the k best, sorted, and writes the row's output.
-//   4. verify     the result is exact iff at least k candidates were found and no buffer overflowed:
-//                 every element outside the candidates ranks below all of them.  Otherwise the row is
-//                 flagged and a second launch -- the scanning kernels of topk.cu, which need no
-//                 assumption -- redoes exactly the flagged rows.  Rows whose beginning says nothing
-//                 about the rest (sorted rows, all-equal rows, rows with fewer than k numbers) go
-//                 that way; they cost a second pass, never a wrong answer.
+//                 the CTA's shared memory, one atomic each.  The sample tiles are scanned first, while
+//                 they are still in L2.
+//   3. merge      the S CTAs of a row are one thread-block cluster.  A CTA that has finished its
+//                 slice reserves room in the candidate buffer of the cluster's first CTA with one
+//                 remote atomic (from the top down, while the first CTA may still be filling it from
+//                 the bottom up), copies its words there with plain remote stores and reports its
+//                 threshold key; one cluster barrier later the first CTA holds the candidates of the
+//                 row.  Every CTA took all elements at or above its own key, so the union holds every
+//                 element at or above the LARGEST of these keys, T*.
+//   4. verify     the first CTA cuts the candidates to the k best, sorted.  The result is exact iff
+//                 no buffer overflowed and the k-th best candidate has a key of at least T*: then at
+//                 least k elements reach T*, all of them are candidates, and everything that is not a
+//                 candidate ranks below them.  Otherwise the row is flagged and a second launch -- the
+//                 scanning kernels of topk.cu, which need no assumption -- redoes exactly the flagged
+//                 rows.  Rows whose beginning says nothing about the rest (sorted rows, all-equal rows,
+//                 rows with fewer than k numbers) go that way; they cost a second pass, never a wrong
+//                 answer.
 //
-// Splitting a row costs nothing here (the threshold does not depend on the scan), so the planner
-// uses as many slices as fill the GPU: clusters of 2 to 8 CTAs per row.  No TMA, no multicast: the
-// cluster is used for its barrier and for remote shared-memory loads and stores only.
+// Splitting a row is cheap here (the threshold does not depend on the scan), so the planner picks
+// CTA width and CTAs per row such that ONE wave of equal CTAs fills the GPU: co-resident CTAs share
+// HBM bandwidth by their loads in flight, so equal CTAs finish together.  No TMA, no multicast: the
+// cluster is used for its barrier and for remote shared-memory atomics and stores only.
 #pragma once
 
 #include <cooperative_groups.h>
@@ -41,48 +50,151 @@ namespace tpb {
 
 namespace cg = cooperative_groups;
 
-constexpr int kSelKeys = 128;        // lane-maximum keys that every CTA offers to the estimate
+// Development builds (-DTPB200_TRACE) stamp the phases of every CTA with %globaltimer; the library
+// then exports tpb200_debug_trace() to read the stamps back.  Ordinary builds compile none of it.
+#ifdef TPB200_TRACE
+constexpr int kTraceCtas = 4096, kTraceSlots = 16;
+__device__ long long g_sel_trace[kTraceCtas * kTraceSlots];
+__device__ __forceinline__ long long sel_now() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TPB_STAMP(i) do { if (threadIdx.x == 0) g_sel_trace[(blockIdx.x % kTraceCtas) * kTraceSlots + (i)] = sel_now(); } while (0)
+#define TPB_NOTE(i, v) do { if (threadIdx.x == 0) g_sel_trace[(blockIdx.x % kTraceCtas) * kTraceSlots + (i)] = (long long)(v); } while (0)
+#else
+#define TPB_STAMP(i) do { } while (0)
+#define TPB_NOTE(i, v) do { } while (0)
+#endif
+
+constexpr int kSelKeys = 128;        // lane-maximum keys that enter a CTA's estimate
 constexpr int kSelMaxCluster = 8;    // portable cluster size
 
 struct SelGeom {
     int S;           // CTAs (slices) per row = cluster size (1, 2, 4 or 8)
-    int r;           // 1-based rank of the threshold key among the sample's lane maxima
-    int cap;         // candidate words per CTA buffer (power of two); also the limit per row
-    int prefetch;    // tiles per warp hinted into L2 before the threshold is known
+    int r;           // 1-based rank of the threshold key among a CTA's lane maxima
+    int cap;         // candidate words of a CTA's buffer; also the limit per row
+    int tpw;         // sample tiles per warp
     int trigger;     // 1: let a dependent launch start early (programmatic dependent launch)
     long long chunk; // slice length
 };
 
 struct SelShared {
-    StreamShared cs;                              // scratch of cut()
-    unsigned bootk[kSelKeys];                     // the warps' best lane maxima, as keys
-    unsigned skeys[kSelKeys];                     // the same, sorted descending; read by the cluster
-    unsigned allk[kSelMaxCluster * kSelKeys];     // the sorted lists of all CTAs of the row
-    unsigned tkey;                                // threshold key (0: no usable threshold)
-    int cnt;                                      // candidates reserved by this CTA (may exceed cap)
-    int next;                                     // next warp-tile of the slice
-    int base, total, bad;                         // merge: offset in the first CTA's buffer, row total, verdict
+    unsigned long long samp[128];   // pivot sample of the final cut
+    unsigned bootk[kSelKeys];       // the warps' best lane maxima, as keys
+    unsigned skeys[kSelKeys];       // the same, sorted descending
+    unsigned tmax;                  // first CTA: largest threshold key reported by the other CTAs
+    int cnt;                        // candidates reserved by this CTA (may exceed cap)
+    int next;                       // next warp-tile of the slice
+    int rem;                        // first CTA: words reserved by the other CTAs, from the top down
+    int bad;                        // first CTA: a CTA of the row had no threshold or overflowed
+    int base;                       // this CTA's reservation in the first CTA's buffer
+    int tmp;
 };
 
-// Entries of the descending list a[0..128) that are greater than / at least `key`.
-__device__ __forceinline__ int sel_count_gt(const unsigned* a, unsigned key) {
-    int lo = 0, hi = kSelKeys;
-    while (lo < hi) { const int mid = (lo + hi) >> 1; if (a[mid] > key) lo = mid + 1; else hi = mid; }
-    return lo;
-}
-__device__ __forceinline__ int sel_count_ge(const unsigned* a, unsigned key) {
-    int lo = 0, hi = kSelKeys;
-    while (lo < hi) { const int mid = (lo + hi) >> 1; if (a[mid] >= key) lo = mid + 1; else hi = mid; }
-    return lo;
+// The first CTA's last step: cut the n candidates in cand[0..n) to the k best, sorted, verify the
+// k-th against the row's threshold key `tstar`, write the row.  Called by every thread of the CTA;
+// returns true when the row must be redone.
+//   n <= 256              every candidate counts the candidates above it: its rank is its output slot
+//   n within 2x of k      CTA-wide bitonic sort of the padded buffer
+//   otherwise             a pivot from a sorted sample of 128 candidates is tried until between k and
+//                         two sort blocks of candidates reach it; those are compacted to the front
+//                         in place and sorted
+template <bool LARGEST, int NT>
+__device__ bool sel_final(unsigned long long* cand, int n, int k, int cap, unsigned tstar, SelShared& sh,
+                          const float* row, long long es, float* ov, long long* oi) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    auto emit = [&](int j, unsigned long long w) {
+        const unsigned idx = word_index(w);
+        float val = key_value<LARGEST>((unsigned)(w >> 32));
+        if (val == 0.0f) val = row[(long long)idx * es];   // the key folds -0.0 onto +0.0: the sign comes from the row
+        oi[j] = (long long)idx;
+        ov[j] = val;
+    };
+    if (tid == 0) sh.tmp = 0;
+    __syncthreads();
+    if (n <= 256) {
+        // P threads share a candidate: each counts over its part of the list (whole warps take part,
+        // so the shuffles are safe; a thread past the list works on word 0 and writes nothing)
+        constexpr int P = NT >= 512 ? 2 : 1;
+        const int step = (n + P - 1) / P;
+        for (int i0 = 0; i0 < n; i0 += NT / P) {
+            const int i = i0 + tid / P, part = tid % P;
+            const unsigned long long w = i < n ? cand[i] : 0ull;
+            int rank = 0;
+            const int j1 = (part + 1) * step < n ? (part + 1) * step : n;
+#pragma unroll 4
+            for (int j = part * step; j < j1; ++j) rank += cand[j] > w ? 1 : 0;
+            if (P >= 2) rank += __shfl_xor_sync(kFull, rank, 1);
+            if (i < n && part == 0 && rank < k) {
+                if (rank == k - 1 && (unsigned)(w >> 32) < tstar) sh.tmp = 1;
+                emit(rank, w);
+            }
+        }
+        __syncthreads();
+        return sh.tmp != 0;
+    }
+    const int Nk = pow2_ceil_dev(k);
+    int m = n;
+    if (!(pow2_ceil_dev(n) <= 2 * Nk && pow2_ceil_dev(n) <= cap)) {
+        // pivot from a sorted sample
+        if (tid < 32) {
+            unsigned long long v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = cand[(long long)(tid * 4 + e) * n / 128];
+            warp_sort_desc<4>(v, tid);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sh.samp[tid * 4 + e] = v[e];
+        }
+        __syncthreads();
+        const int most = 2 * Nk < cap ? 2 * Nk : cap;
+        // sample rank whose pivot is expected to keep about 1.19 k + 24 words
+        int q = (int)(((long long)128 * (k + (k >> 3) + (k >> 4) + 24) + n - 1) / n) + 1;
+        bool ok = false;
+        unsigned long long pivot = 0ull;
+        for (int attempt = 0; attempt < 4 && q <= 127; ++attempt, q += 6) {
+            pivot = sh.samp[q];
+            int cnt = 0;
+            for (int i = tid; i < n; i += NT) cnt += cand[i] >= pivot ? 1 : 0;
+            cnt = __reduce_add_sync(kFull, cnt);
+            if (lane == 0 && cnt) atomicAdd(&sh.tmp, cnt);
+            __syncthreads();
+            const int total = sh.tmp;
+            __syncthreads();
+            if (tid == 0) sh.tmp = 0;
+            __syncthreads();
+            if (total >= k && total <= most) { ok = true; m = total; break; }
+        }
+        if (!ok) {
+            if (pow2_ceil_dev(n) > cap) return true;   // no pivot fits and no room to sort everything: redo
+        } else {
+            // compact the words >= pivot to the front, in place: a word only ever moves to a lower
+            // position, and a batch is read completely before any of it is written
+            for (int base = 0; base < n; base += NT) {
+                const int i = base + tid;
+                const unsigned long long w = i < n ? cand[i] : 0ull;
+                const bool keep = w >= pivot;   // pivot > 0, so padding never passes
+                const unsigned bal = __ballot_sync(kFull, keep);
+                int wb = 0;
+                __syncthreads();
+                if (lane == 0 && bal) wb = atomicAdd(&sh.tmp, __popc(bal));
+                wb = __shfl_sync(kFull, wb, 0);
+                if (keep) cand[wb + __popc(bal & ((1u << lane) - 1u))] = w;
+            }
+            __syncthreads();
+        }
+    }
+    const int N = pow2_ceil_dev(m) < 2 ? 2 : pow2_ceil_dev(m);
+    for (int i = m + tid; i < N; i += NT) cand[i] = 0ull;
+    __syncthreads();
+    bitonic_desc(cand, N, tid, NT);
+    if ((unsigned)(cand[k - 1] >> 32) < tstar) return true;
+    for (int j = tid; j < k; j += NT) emit(j, cand[j]);
+    return false;
 }
 
 template <bool LARGEST, bool VEC, int NW>
 __global__ void __launch_bounds__(NW * 32, NW == 4 ? 7 : (NW == 8 ? 4 : 2))
 topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* __restrict__ out_val,
-                   long long* __restrict__ out_idx, int* __restrict__ fail) {
+                   long long* __restrict__ out_idx, int* __restrict__ redo) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned long long* cand = reinterpret_cast<unsigned long long*>(smem_raw);   // cap words
-    unsigned long long* buf2 = cand + sg.cap;                                     // cap / 2 words (cut's partition target)
     __shared__ SelShared sh;
     constexpr int NT = NW * 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -99,8 +211,16 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
     const int ntiles = (int)((len + kWarpTile - 1) / kWarpTile);
     const int k = (int)g.k, cap = sg.cap;
 
-    if (tid == 0) { sh.tkey = 0u; sh.cnt = 0; sh.next = NW; sh.base = 0; sh.total = 0; sh.bad = 0; }
+    TPB_STAMP(0);
+    if (tid == 0) { sh.tmax = 0u; sh.cnt = 0; sh.next = 0; sh.rem = 0; sh.bad = 0; sh.base = 0; sh.tmp = 0; }
+    // The other CTAs of the row write to this CTA's shared memory at the end of their scan; they must
+    // see it initialised.  Arrive at the cluster barrier now (the release orders the line above) and
+    // wait for it only after the scan, when every CTA has long arrived: the barrier costs nothing.
+    if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     if (sg.trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // as a dependent launch this kernel may have started before the previous kernel of the stream
+    // has finished: nothing is read or written before this point
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     auto elem_off = [&](long long off, int j) -> long long { return off + ((j >> 2) * 32 + lane) * 4 + (j & 3); };
     // A tile in registers; elements past the end of the slice read as NaN (never a candidate).
@@ -148,24 +268,23 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
         }
     };
 
-    // ---- 1. sample: this warp's first tile stays in registers until the threshold is known
-    float4 v0[8];
-    const long long off0 = (long long)warp * kWarpTile;
-    load_tile(v0, off0);
-    if (VEC) {
-        // hint the tiles that this CTA scans next into L2 while the threshold is being found
-        for (int i = 0; i < sg.prefetch; ++i) {
-            const long long t = (long long)NW * (1 + i) + warp;
-            if ((t + 1) * kWarpTile <= len) asm volatile("prefetch.global.L2 [%0];" ::"l"(slice + t * kWarpTile + lane * 32));
-        }
-    }
-    {
-        float mx = NAN;   // fmaxf / fminf ignore a NaN operand
+    // ---- 1. sample: one maximum per lane over this warp's first tpw tiles; nothing is kept
+    float4 v[8];
+    float mx = NAN;   // fmaxf / fminf ignore a NaN operand
+    for (int t = 0; t < sg.tpw; ++t) {
+        load_tile(v, (long long)(t * NW + warp) * kWarpTile);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            if (LARGEST) mx = fmaxf(fmaxf(mx, v0[u].x), fmaxf(fmaxf(v0[u].y, v0[u].z), v0[u].w));
-            else         mx = fminf(fminf(mx, v0[u].x), fminf(fminf(v0[u].y, v0[u].z), v0[u].w));
+            if (LARGEST) mx = fmaxf(fmaxf(mx, v[u].x), fmaxf(fmaxf(v[u].y, v[u].z), v[u].w));
+            else         mx = fminf(fminf(mx, v[u].x), fminf(fminf(v[u].y, v[u].z), v[u].w));
         }
+    }
+    TPB_STAMP(1);
+    // the first scan tile of this warp: its loads are in flight while the threshold is worked out
+    const int first_scan = sg.tpw * NW;               // tiles [first_scan, first_scan + NW) are taken here
+    const long long off_b = (long long)(first_scan + warp) * kWarpTile;
+    load_tile(v, off_b);
+    {
         unsigned key = rank_key<LARGEST>(mx);
 #pragma unroll
         for (int size = 2; size <= 32; size <<= 1) {
@@ -180,107 +299,97 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
         if (lane < kShare) sh.bootk[warp * kShare + lane] = key;
     }
     __syncthreads();
-    if (tid < kSelKeys) {   // rank sort of the CTA's 128 keys (ties by position)
-        const unsigned my = sh.bootk[tid];
-        int pos = 0;
-        for (int i = 0; i < kSelKeys; ++i) {
-            const unsigned o = sh.bootk[i];
-            pos += (o > my || (o == my && i < tid)) ? 1 : 0;
-        }
-        sh.skeys[pos] = my;
-    }
-    __syncthreads();
-    if (S > 1) {
-        cluster.sync();
-        for (int i = tid; i < S * kSelKeys; i += NT) {
-            const unsigned* rk = cluster.map_shared_rank(sh.skeys, (unsigned)(i / kSelKeys));
-            sh.allk[i] = rk[i % kSelKeys];
-        }
-        __syncthreads();
-        for (int i = tid; i < S * kSelKeys; i += NT) {
-            const unsigned my = sh.allk[i];
-            int gt = 0, ge = 0;
-            for (int l = 0; l < S; ++l) {
-                gt += sel_count_gt(sh.allk + l * kSelKeys, my);
-                ge += sel_count_ge(sh.allk + l * kSelKeys, my);
+    {   // rank sort of the CTA's 128 keys (ties by position), P threads per key
+        constexpr int P = NT >= 512 ? 4 : (NT >= 256 ? 2 : 1);
+        const int i = tid / P, part = tid % P;
+        if (i < kSelKeys) {
+            const unsigned my = sh.bootk[i];
+            int pos = 0;
+#pragma unroll 8
+            for (int j = part * (kSelKeys / P); j < (part + 1) * (kSelKeys / P); ++j) {
+                const unsigned o = sh.bootk[j];
+                pos += (o > my || (o == my && j < i)) ? 1 : 0;
             }
-            if (gt < sg.r && sg.r <= ge) sh.tkey = my;   // the same value from every writer
+            if (P >= 2) pos += __shfl_xor_sync(kFull, pos, 1);
+            if (P >= 4) pos += __shfl_xor_sync(kFull, pos, 2);
+            if (part == 0) sh.skeys[pos] = my;
         }
-    } else if (tid == 0) {
-        sh.tkey = sh.skeys[sg.r - 1];
     }
     __syncthreads();
-    const unsigned tkey = sh.tkey;
+    const unsigned tkey = sh.skeys[sg.r - 1];
+    TPB_STAMP(2);
     // key 0 is the rank of NaN: the sample held fewer than r numbers, there is no float threshold
     const bool no_threshold = tkey == 0u;
 
-    // ---- 2. scan
+    // ---- 2. scan: the tile already loaded, then the sample tiles (still in L2), then the rest
     if (!no_threshold) {
         const float tvf = key_value<LARGEST>(tkey);
-        append(mask_of(v0, tvf), off0);
+        append(mask_of(v, tvf), off_b);
         for (;;) {
             int t = 0;
             if (lane == 0) t = atomicAdd(&sh.next, 1);
             t = __shfl_sync(kFull, t, 0);
+            if (t >= first_scan) t += NW;
             if (t >= ntiles) break;
             const long long off = (long long)t * kWarpTile;
             unsigned m;
             {
-                float4 v[8];
-                load_tile(v, off);
-                m = mask_of(v, tvf);
+                float4 w[8];
+                load_tile(w, off);
+                m = mask_of(w, tvf);
             }
             append(m, off);
         }
     }
     __syncthreads();
+    if (S > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    TPB_STAMP(3);
+    TPB_NOTE(8, sh.cnt);
 
     // ---- 3. merge the CTAs of the row into the first one
     int n = sh.cnt;
     bool bad = no_threshold || n > cap;
     if (n > cap) n = cap;
+    unsigned tstar = tkey;
     if (S > 1) {
-        cluster.sync();   // every CTA of the row has finished its scan
-        if (tid == 0) {
-            int base = 0, total = 0, over = 0;
-            for (int q = 0; q < S; ++q) {
-                int cn = *cluster.map_shared_rank(&sh.cnt, (unsigned)q);
-                if (cn > cap) { over = 1; cn = cap; }
-                if (q < c) base += cn;
-                total += cn;
+        if (c > 0) {
+            if (tid == 0) {
+                sh.base = atomicAdd(cluster.map_shared_rank(&sh.rem, 0u), n);
+                atomicMax(cluster.map_shared_rank(&sh.tmax, 0u), tkey);
+                if (bad) atomicOr(cluster.map_shared_rank(&sh.bad, 0u), 1);
             }
-            sh.base = base;
-            sh.total = total;
-            sh.bad = (over || total > cap) ? 1 : 0;
+            __syncthreads();
+            const int base = sh.base;
+            if (base + n <= cap) {   // otherwise the row has overflowed; the first CTA sees it from `rem`
+                unsigned long long* dst = cluster.map_shared_rank(cand, 0u) + (cap - base - n);
+                for (int i = tid; i < n; i += NT) dst[i] = cand[i];
+            }
+            cluster.sync();   // the remote stores are complete and visible to the first CTA
+            TPB_STAMP(4);
+            return;
+        }
+        cluster.sync();
+        const int rem = sh.rem;
+        bad = bad || sh.bad != 0 || n + rem > cap;
+        if (sh.tmax > tstar) tstar = sh.tmax;
+        if (!bad) {
+            // own words in [0, n), the others' in [cap - rem, cap): close the gap with words from the top
+            const int gap = cap - rem - n;
+            const int mv = rem < gap ? rem : gap;
+            for (int i = tid; i < mv; i += NT) cand[n + i] = cand[cap - mv + i];
+            n += rem;
         }
         __syncthreads();
-        bad = bad || sh.bad != 0;
-        if (!bad && c > 0) {
-            unsigned long long* dst = cluster.map_shared_rank(cand, 0u) + sh.base;
-            for (int i = tid; i < n; i += NT) dst[i] = cand[i];
-        }
-        cluster.sync();   // remote stores done; nobody reads this CTA's shared memory any more
-        if (c > 0) return;
-        n = sh.total;
+        TPB_STAMP(4);
     }
 
-    // ---- 4. verify; cut to the k best, sorted; write the row
+    // ---- 4. cut, verify, write
     bad = bad || n < k;
-    if (tid == 0) fail[r] = bad ? 1 : 0;
-    if (bad) return;   // the second launch redoes this row
-    if (tid == 0) sh.cs.cnt = n;
-    __syncthreads();
-    cut(cand, buf2, &sh.cs, cap, k, tid, NT, true);
-    for (int j = tid; j < k; j += NT) {
-        const unsigned long long w = cand[j];
-        const unsigned idx = word_index(w);
-        const unsigned key = (unsigned)(w >> 32);
-        float val = key_value<LARGEST>(key);
-        // the key folds -0.0 onto +0.0: the sign comes from the row
-        if (val == 0.0f) val = row[(long long)idx * g.es];
-        out_idx[r * k + j] = (long long)idx;
-        out_val[r * k + j] = val;
-    }
+    TPB_NOTE(9, n);
+    TPB_STAMP(5);
+    if (!bad) bad = sel_final<LARGEST, NT>(cand, n, k, cap, tstar, sh, row, g.es, out_val + r * k, out_idx + r * k);
+    if (tid == 0) redo[r] = bad ? 1 : 0;
+    TPB_STAMP(7);
 }
 
 }  // namespace tpb

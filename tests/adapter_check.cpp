@@ -16,6 +16,10 @@
 
 using namespace tensorplay;
 
+// the CPU checker's top-k (oracle/tp_oracle.c): [rows, len] with strides in elements -> [rows, k]
+extern "C" int tpo_topk(const float* in, int64_t rows, int64_t len, int64_t row_stride, int64_t elem_stride,
+                        int64_t k, int largest, float* out_val, int64_t* out_idx);
+
 static Tensor to_cuda(const Tensor& c) {
     Tensor g(static_cast<std::vector<int64_t>>(c.shape()), c.dtype(), Device(DeviceType::CUDA, 0));
     cudaMemcpy(g.data_ptr(), c.data_ptr(), c.numel() * c.itemsize(), cudaMemcpyHostToDevice);
@@ -109,6 +113,44 @@ int main() {
     equal_bool("any(dim=0,keepdim)", gw.any({0}, true), cw.any({0}, true));
     equal_bool("all()", gw.all(), cw.all());
     equal_bool("any()", gw.any(), cw.any());
+    // topk: not declared by the reference; the schema entry beside the adapter adds Tensor::topk, which
+    // must reach the new kernel through the Dispatcher.  Expected values from the CPU checker on the
+    // host copy: last dim and a non-last dim, both directions, with ties (v[7] == v[3]) and a
+    // tie-heavy row.
+    {
+        std::vector<float> tv(v);
+        for (int64_t j = 0; j < C; ++j) tv[9 * C + j] = (float)(j % 5);       // row 9: 200 copies of each value
+        Tensor ct2 = Tensor::tensor<float>(tv).reshape({R, C});
+        Tensor gt2 = to_cuda(ct2);
+        for (int largest = 0; largest < 2; ++largest) {
+            const int64_t k = 17;
+            auto [vals, idx] = gt2.topk(k, -1, largest != 0, true);
+            std::vector<float> wv(R * k);
+            std::vector<int64_t> wi(R * k);
+            tpo_topk(tv.data(), R, C, C, 1, k, largest, wv.data(), wi.data());
+            ++checks;
+            auto hv = to_host<float>(vals);
+            auto hi = to_host<int64_t>(idx);
+            if (static_cast<std::vector<int64_t>>(vals.shape()) != std::vector<int64_t>{R, k} || idx.dtype() != DType::Int64 ||
+                std::memcmp(hv.data(), wv.data(), wv.size() * 4) != 0 || hi != wi) { printf("FAIL topk(dim=-1, largest=%d)\n", largest); ++fails; }
+            // along dim 0: rows are the columns of the matrix, read with stride C
+            const int64_t k0 = 5;
+            auto [vals0, idx0] = gt2.topk(k0, 0, largest != 0, true);
+            std::vector<float> wv0(C * k0);
+            std::vector<int64_t> wi0(C * k0);
+            tpo_topk(tv.data(), C, R, 1, C, k0, largest, wv0.data(), wi0.data());
+            ++checks;
+            // the result is a [k0, C] view of storage laid out [C, k0]
+            auto hv0 = to_host<float>(vals0);
+            auto hi0 = to_host<int64_t>(idx0);
+            if (static_cast<std::vector<int64_t>>(vals0.shape()) != std::vector<int64_t>{k0, C} || vals0.strides() != std::vector<int64_t>{1, k0} ||
+                std::memcmp(hv0.data(), wv0.data(), wv0.size() * 4) != 0 || hi0 != wi0) { printf("FAIL topk(dim=0, largest=%d)\n", largest); ++fails; }
+        }
+        auto [v1, i1] = Tensor::topk(gt2, 1, 1, true, true);                  // function variant; k = 1 is argmax
+        equal_i("topk(k=1) indices == argmax", i1.reshape({R}), ct2.argmax(std::optional<int64_t>(1), false));
+        try { gt2.topk(C + 1, -1, true, true); printf("FAIL: no error for k > len\n"); ++fails; }
+        catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "selected index k out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }
+    }
     // errors keep the reference's type and message
     try { g.sum({2}, false, DType::Undefined); printf("FAIL: no error for a bad dim\n"); ++fails; }
     catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "Dimension out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }

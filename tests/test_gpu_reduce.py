@@ -226,8 +226,8 @@ def test_forced_row_strategies(cuda, strategy, monkeypatch):
         check(cuda, flat, op, None, what=strategy)
 
 
-def test_config1_rowwise(cuda):
-    """BASELINE config 1: [4096, 4096] N(0,1), seed 0; sum/mean/var/max/argmax over dim -1."""
+def test_rowwise_4096x4096(cuda):
+    """[4096, 4096] N(0,1), seed 0, full size; sum/mean/var/std/max/min/argmax/argmin over dim -1."""
     x = config1()
     for op in ["sum", "mean", "var", "std", "max", "min", "argmax", "argmin"]:
         check(cuda, x, op, [-1])
@@ -239,23 +239,78 @@ def test_config1_rowwise(cuda):
     assert torch.equal(v, xg.gather(1, i[:, None])[:, 0])
 
 
-def test_config3_nonlast(cuda):
-    """BASELINE config 3 at a quarter of its batch ([16, 4096, 512], same generator and seed):
-    sum/mean/max/argmin over dim 1, sum/std over dims (0, 2)."""
-    x = config3(a=16)
+def test_nonlast_dims_64x4096x512(cuda):
+    """[64, 4096, 512] uniform(-1, 1), seed 2, full size: sum/mean/max/argmin (and var, min, argmax)
+    over dim 1, sum/std (and mean, max) over dims (0, 2)."""
+    x = config3()
     for op in ["sum", "mean", "max", "min", "argmin", "argmax", "var"]:
         check(cuda, x, op, [1])
     for op in ["sum", "std", "mean", "max"]:
         check(cuda, x, op, [0, 2])
 
 
-def test_whole_tensor_large(cuda):
-    """Whole-tensor reductions with the value distribution of BASELINE config 4 (uniform(-1,1),
-    1% of positions +-1e4) on 2^26+5 elements: the oracle finishes in seconds at this size."""
+def test_whole_tensor_2_to_26(cuda):
+    """Whole-tensor reductions of 2^26+5 elements, uniform(-1,1) with 1% of positions +-1e4, against
+    the oracle element for element."""
     from util import config4
     x = config4(n=(1 << 26) + 5)
     for op in ["sum", "mean", "var", "std", "max", "min", "argmax", "argmin"]:
         check(cuda, x, op, None)
+
+
+def test_whole_tensor_2_to_31(cuda):
+    """The full 2^31-element tensor (8 GiB; the element count does not fit int32): uniform(-1,1) with
+    1% of positions +-1e4, made chunk by chunk on the device.  sum / mean / var / std against a
+    float64 evaluation merged over the chunks with Chan's update (torch float64 per chunk, tied to
+    numpy float64 on the first and the last chunk); max / min / argmax / argmin exact.  A maximum is
+    planted a few hundred elements before the end (the last slice) and tied by an element in the
+    first half: the lower index must win; then the tie is removed and the late one must be found."""
+    import torch
+    import tensorplay_b200 as tpb
+
+    n, chunk = 1 << 31, 1 << 26
+    late, early = n - 700, (n >> 1) - 12345
+    lo_pos = n - 5                                   # the minimum sits in the very last vector
+    xg = torch.empty(n, dtype=torch.float32, device=cuda)
+    gen = torch.Generator(device=cuda).manual_seed(3)
+    cnt, mean, m2 = 0.0, 0.0, 0.0
+    for s in range(0, n, chunk):
+        v = torch.rand(chunk, device=cuda, generator=gen) * 2.0 - 1.0
+        sel = torch.rand(chunk, device=cuda, generator=gen)
+        v = torch.where(sel < 0.005, torch.full_like(v, 1e4), v)
+        v = torch.where(sel > 0.995, torch.full_like(v, -1e4), v)
+        for p, val in ((late, 3e4), (early, 3e4), (lo_pos, -3e4)):
+            if s <= p < s + chunk:
+                v[p - s] = val
+        xg[s:s + chunk] = v
+        v64 = v.double()
+        cm = float(v64.mean().item())
+        cm2 = float(((v64 - cm) ** 2).sum().item())
+        if s == 0 or s + chunk == n:                 # the float64 evaluation itself, against numpy
+            h = v.cpu().numpy().astype(np.float64)
+            assert abs(h.mean() - cm) <= 1e-12 * max(1.0, abs(cm)) + 1e-9
+            assert abs(((h - h.mean()) ** 2).sum() - cm2) <= 1e-9 * cm2
+        tot = cnt + chunk
+        delta = cm - mean
+        m2 = m2 + cm2 + delta * delta * cnt * chunk / tot
+        mean = mean + delta * chunk / tot
+        cnt = tot
+        del v, sel, v64
+    truth = {"sum": mean * n, "mean": mean, "var": m2 / (n - 1), "std": float(np.sqrt(m2 / (n - 1)))}
+    for op in ("sum", "mean", "var", "std"):
+        got = float(getattr(tpb, op)(xg).item())
+        assert abs(got - truth[op]) <= 1e-5 * abs(truth[op]), (op, got, truth[op])
+    assert tpb.max(xg).item() == 3e4 and tpb.min(xg).item() == -3e4
+    assert tpb.argmax(xg).item() == early
+    assert tpb.argmin(xg).item() == lo_pos
+    v, i = tpb.max_with_indices(xg.view(1, n), 1)
+    assert v.item() == 3e4 and i.item() == early
+    xg[early] = 0.5
+    assert tpb.argmax(xg).item() == late
+    from tensorplay_b200 import _lib
+    assert _lib.device_status() == 0
+    del xg
+    torch.cuda.empty_cache()
 
 
 def test_run_to_run_bit_identity(cuda):

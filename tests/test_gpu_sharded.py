@@ -125,6 +125,42 @@ def test_fused_exchange_one_rank(cuda):
     assert _lib.device_status() == 0
 
 
+def test_fused_exchange_wait_runs_out(cuda):
+    """A rank whose peer never arrives: the wait is bounded, the kernel returns by itself with status 5
+    and poisoned outputs (NaN / -1, not the previous call's answer), and the next call works.  Rank 1
+    of a two-rank exchange simply never runs here; nothing faults or hangs."""
+    import ctypes
+    import torch
+    import tensorplay_b200 as tpb
+    from tensorplay_b200 import _lib
+    L = _lib.lib()
+    x = torch.arange(1 << 20, dtype=torch.float32, device=cuda)
+    n = x.numel()
+    nb = L.tpb200_exchange_buffer_bytes()
+    bufs = [torch.zeros(nb, dtype=torch.uint8, device=cuda) for _ in range(2)]
+    peers = (ctypes.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+    ws = torch.empty(max(8, L.tpb200_reduce_partial_workspace_bytes(_lib.OP["sum"], 0, n)), dtype=torch.uint8, device=cuda)
+    ov = torch.full((1,), 123.0, device=cuda)          # stands for the previous call's answer
+    oi = torch.full((1,), 456, dtype=torch.int64, device=cuda)
+    st = torch.cuda.current_stream().cuda_stream
+    assert _lib.device_status() == 0
+    _lib.check(L.tpb200_set_exchange_wait_polls(2000))          # a fraction of a millisecond
+    try:
+        _lib.check(L.tpb200_reduce_fused_exchange(_lib.OP["max_argmax"], x.data_ptr(), 0, n, 0, 2 * n, 1, 0, 2, peers,
+                                                  ov.data_ptr(), oi.data_ptr(), ws.data_ptr(), ws.numel(), st))
+        assert _lib.device_status() == 5                           # synchronises; reads and clears the word
+        assert torch.isnan(ov).item() and oi.item() == -1
+        assert _lib.device_status() == 0
+    finally:
+        _lib.check(L.tpb200_set_exchange_wait_polls(1 << 22))
+    assert L.tpb200_set_exchange_wait_polls(0) == _lib.ERR_INVALID
+    # a fresh single-rank exchange right after it
+    red = tpb.ShardedReducer(cuda, fused=True)
+    v, i = red.reduce("max_argmax", x, 0, n)
+    assert v.item() == float(n - 1) and i.item() == n - 1
+    assert _lib.device_status() == 0
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))

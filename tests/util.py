@@ -43,8 +43,25 @@ def config4(n=1 << 31, chunk=1 << 24):
     return out
 
 
+_config5_cache = {}
+
+
 def config5(rows=512, cols=1 << 20):
-    return np.random.default_rng(4).integers(0, 1000, (rows, cols)).astype(np.float32)
+    """Integers 0..999 as float (tie-heavy).  The full-size array (2 GiB) is kept for the second test
+    that asks for it; generated block by block so that the int64 draw never exists whole."""
+    key = (rows, cols)
+    if key not in _config5_cache:
+        rng = np.random.default_rng(4)
+        if rows * cols <= (1 << 26):
+            x = rng.integers(0, 1000, (rows, cols)).astype(np.float32)
+        else:
+            x = np.empty((rows, cols), dtype=np.float32)
+            step = max(1, (1 << 26) // cols)
+            for r in range(0, rows, step):
+                x[r:r + step] = rng.integers(0, 1000, (min(step, rows - r), cols))
+        _config5_cache.clear()
+        _config5_cache[key] = x
+    return _config5_cache[key]
 
 
 def bits(a: np.ndarray) -> np.ndarray:
