@@ -59,6 +59,55 @@ inline bool env_int(const char* name, int* out) {
     return true;
 }
 
+// Programmatic dependent launch of the sampled-threshold top-k kernel: off unless TPB200_PDL=1 (with
+// TPB200_EXPERIMENTS set).  Measured on one B200, kernels back to back in one CUDA graph: it bought
+// 0.2 us of 33 us on [256,151936] k = 50 and 2 us of 162 us on a 2^28-element sum, nothing on the
+// [4096,4096] row reductions, and the two griddepcontrol instructions at the top of a kernel cost
+// every CTA about 2 us on kernels of many short CTAs ([64,4096,512] summed over dims (0,2): 76.5 us
+// without them, 94.8 us with them, whether or not the launch carried the attribute).  The reductions
+// therefore launch the ordinary way and execute no such instruction.
+inline bool dependent_launch_on() {
+    int v = 0;
+    env_int("TPB200_PDL", &v);
+    return v != 0;
+}
+
+// One launch through cudaLaunchKernelEx.  `cluster` > 1 makes clusters of that many CTAs along x.
+// `dependent` lets the kernel start before the previous kernel of the stream has finished; such a
+// kernel must wait (griddepcontrol.wait) before it touches memory.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, int threads, size_t smem, cudaStream_t st,
+                             int cluster, bool dependent, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    unsigned na = 0;
+    if (cluster > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)cluster;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (dependent) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define TPB_LAUNCH(name, kernel, grid, threads, smem, st, ...)                                                    \
+    do {                                                                                                          \
+        cudaError_t e__ = ::tpb::launch_ex(kernel, grid, threads, smem, st, 1, false, __VA_ARGS__);                 \
+        if (e__ != cudaSuccess) return ::tpb::cuda_fail(e__, name);                                               \
+    } while (0)
+
 inline long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 inline long long round_up(long long a, long long b) { return ceil_div(a, b) * b; }
 inline int pow2_ceil(long long v) {

@@ -127,20 +127,25 @@ row_cta_kernel(const float* __restrict__ in, RowGeom g, int tps, int vec_ok, Epi
 }
 
 // ------------------------------------------------------------------ ROW: split rows --------
-// Pass 1: CTA (s, r) reduces the fixed slice [s*chunk, (s+1)*chunk) of row r to one packed partial.
+// Pass 1: S CTAs per row, all resident at once.  CTA s of row r reduces the blocks s, s + S, s + 2S,
+// ... of `sub` elements each to ONE packed partial: the CTAs of a row walk through it side by side
+// and finish together, so there is one ramp and one tail per launch instead of one per wave of
+// slices (measured on 2^28 elements: contiguous slices in four waves 163-169 us).  The
+// assignment of blocks to CTAs and the order inside a thread are fixed, so results stay
+// bit-reproducible; every thread still sees its elements in ascending position.
 template <class Acc>
 __global__ void __launch_bounds__(512)
-row_split_kernel(const float* __restrict__ in, RowGeom g, long long chunk, Packed* ws) {
+row_split_kernel(const float* __restrict__ in, RowGeom g, long long sub, int S, Packed* ws) {
     __shared__ Acc sm[32];
     const int tid = threadIdx.x, nthr = blockDim.x;
-    const long long s = blockIdx.x, r = blockIdx.y, S = gridDim.x;
+    const long long s = blockIdx.x % (unsigned)S, r = blockIdx.x / (unsigned)S;
     const float* p = row_base(in, g, r);
-    const long long begin = s * chunk;
-    long long end = begin + chunk;
-    if (end > g.seglen) end = g.seglen;
     Acc acc;
     acc.init();
-    if (begin < end) scan_contig<4>(acc, p + begin, end - begin, begin, tid, nthr);
+    for (long long b = s * sub; b < g.seglen; b += (long long)S * sub) {
+        const long long len = g.seglen - b < sub ? g.seglen - b : sub;
+        scan_contig<4>(acc, p + b, len, b, tid, nthr);
+    }
     acc.finish_thread();
     block_combine(acc, sm);
     if (tid == 0) acc.store(&ws[r * S + s]);
@@ -360,17 +365,14 @@ static int family_of(int op, Family* f) {
 }
 
 
-// Slices per SM of a split reduction: 16 for long inputs (several waves of CTAs even out what the
-// SMs differ in), fewer when that would make a slice shorter than 256 K elements, where the
-// per-slice epilogue starts to show -- most for the variance, whose epilogue is the heaviest.
-// Measured on one B200, 2^28 elements (one GPU's share of 2^31 at eight GPUs): sum 169 / 163 / 165 us,
-// var 219 / 197 / 184 us, max 180 / 170 / 175 us at 16 / 12 / 8 slices per SM; 2^31 elements:
-// 16 per SM is the fastest for all three (var 1227 us against 1290 us at 8).
-static long long split_slices_per_sm(long long elements, int sms) {
+constexpr long long kSplitBlock = 32768;   // elements per block of a split row: 512 threads x 4 loads of 16 bytes x 4 rounds
+
+// CTAs per SM of a split reduction: as many as are resident at once (four of 512 threads; three for
+// the variance, whose kernel needs 40 registers per thread), so that the whole launch is one wave.
+static long long split_ctas_per_sm(Family fam) {
     int ev = 0;
     if (env_int("TPB200_SPLIT_PER_SM", &ev)) return std::max(1, ev);
-    const long long per = elements / ((long long)sms * 262144);
-    return std::max(4LL, std::min(16LL, (per + 2) / 4 * 4));
+    return fam == FAM_MOM ? 3 : 4;
 }
 
 struct Dim { long long size, stride; };
@@ -399,7 +401,6 @@ static Strategy forced_strategy() {
 
 static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64_t* strides,
                      uint64_t mask, Family fam, Plan* pl) {
-    (void)fam;   // every family plans alike since the variance went to fp32 blocks of four
     if (ndim < 0 || ndim > TPB200_MAX_DIMS)
         return fail(TPB200_ERR_UNSUPPORTED, "tensors of rank %d are not supported (max %d)", ndim, TPB200_MAX_DIMS);
     if (ndim > 0 && (!sizes || !strides)) return fail(TPB200_ERR_INVALID, "sizes/strides must not be NULL");
@@ -456,13 +457,13 @@ static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64
 
         // split: few rows, each long enough to feed many CTAs
         int S = 1;
-        if (g.nseg == 1 && outs <= 65535) {
-            long long want = ceil_div((long long)sms * split_slices_per_sm(L * outs, sms), outs);
+        if (g.nseg == 1 && outs <= 0x3fffff) {
+            long long want = std::max(1LL, (long long)sms * split_ctas_per_sm(fam) / outs);
             long long most = L / 16384;
             S = (int)std::max(1LL, std::min(std::min(want, most), 1LL << 20));
         }
         Strategy st;
-        if (force == ST_ROW_SPLIT && g.nseg == 1 && outs <= 65535) { st = ST_ROW_SPLIT; S = std::max(S, 2); }
+        if (force == ST_ROW_SPLIT && g.nseg == 1 && outs <= 0x3fffff) { st = ST_ROW_SPLIT; S = std::max(S, 2); }
         else if (force == ST_ROW_WARP) st = ST_ROW_WARP;
         else if (force == ST_ROW_CTA) st = ST_ROW_CTA;
         else if (S >= 2) st = ST_ROW_SPLIT;
@@ -473,9 +474,8 @@ static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64
 
         pl->st = st;
         if (st == ST_ROW_SPLIT) {
-            pl->S = S;
-            pl->chunk = round_up(ceil_div(L, S), 4);
-            pl->S = (int)ceil_div(L, pl->chunk);
+            pl->chunk = kSplitBlock;                       // block length of the interleaved walk
+            pl->S = (int)std::max(1LL, std::min<long long>(S, ceil_div(L, pl->chunk)));
             pl->threads = 512;
             pl->ws_bytes = (size_t)outs * pl->S * sizeof(Packed);
         } else if (st == ST_ROW_CTA) {
@@ -530,23 +530,21 @@ static int launch_plan(const Plan& pl, const float* in, Epilogue e, float* ov, l
                 if (a4 <= 10.0 && std::ceil(a4) / a4 < std::ceil(a8) / a8 - 0.02) wpc = 4;
             }
             unsigned grid = (unsigned)ceil_div(pl.row.rows, wpc);
-            row_warp_kernel<Acc><<<grid, wpc * 32, 0, st>>>(in, pl.row, e, ov, oi);
-            TPB_LAUNCH_OK("row_warp_kernel");
+            TPB_LAUNCH("row_warp_kernel", row_warp_kernel<Acc>, dim3(grid), wpc * 32, 0, st, in, pl.row, e, ov, oi);
             return TPB200_OK;
         }
         case ST_ROW_CTA: {
             if (pl.row.rows > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
-            row_cta_kernel<Acc><<<(unsigned)pl.row.rows, pl.threads, 0, st>>>(in, pl.row, pl.tps, pl.vec_ok, e, ov, oi);
-            TPB_LAUNCH_OK("row_cta_kernel");
+            TPB_LAUNCH("row_cta_kernel", row_cta_kernel<Acc>, dim3((unsigned)pl.row.rows), pl.threads, 0, st, in, pl.row, pl.tps, pl.vec_ok, e, ov, oi);
             return TPB200_OK;
         }
         case ST_ROW_SPLIT: {
-            dim3 grid((unsigned)pl.S, (unsigned)pl.row.rows);
-            row_split_kernel<Acc><<<grid, pl.threads, 0, st>>>(in, pl.row, pl.chunk, (Packed*)ws);
-            TPB_LAUNCH_OK("row_split_kernel");
+            if (pl.row.rows * pl.S > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
+            dim3 grid((unsigned)(pl.S * pl.row.rows));
+            TPB_LAUNCH("row_split_kernel", row_split_kernel<Acc>, grid, pl.threads, 0, st, in, pl.row, pl.chunk, pl.S, (Packed*)ws);
             unsigned fg = (unsigned)ceil_div(pl.row.rows, 4);
-            finalize_kernel<Acc><<<fg, 128, 0, st>>>((const Packed*)ws, pl.row.rows, pl.S, (double)pl.count, e, ov, oi, nullptr, 0);
-            TPB_LAUNCH_OK("finalize_kernel");
+            TPB_LAUNCH("finalize_kernel", finalize_kernel<Acc>, dim3(fg), 128, 0, st, (const Packed*)ws, pl.row.rows, pl.S, (double)pl.count, e, ov, oi,
+                       (Packed*)nullptr, 0LL);
             return TPB200_OK;
         }
         case ST_COL: {
@@ -555,23 +553,20 @@ static int launch_plan(const Plan& pl, const float* in, Epilogue e, float* ov, l
             Packed* w = pl.S > 1 ? (Packed*)ws : nullptr;
             if (pl.vec == 4) {
                 size_t sm = (size_t)std::max(1, ny / 2) * pl.tx_n * 4 * sizeof(Acc);
-                col_kernel<Acc, 4><<<grid, 256, sm, st>>>(in, pl.o_stride, pl.L, pl.l_stride, pl.I, pl.tiles, pl.tx_n, pl.lchunk, w, e, ov, oi);
+                TPB_LAUNCH("col_kernel", (col_kernel<Acc, 4>), grid, 256, sm, st, in, pl.o_stride, pl.L, pl.l_stride, pl.I, pl.tiles, pl.tx_n, pl.lchunk, w, e, ov, oi);
             } else {
                 size_t sm = (size_t)std::max(1, ny / 2) * pl.tx_n * sizeof(Acc);
-                col_kernel<Acc, 1><<<grid, 256, sm, st>>>(in, pl.o_stride, pl.L, pl.l_stride, pl.I, pl.tiles, pl.tx_n, pl.lchunk, w, e, ov, oi);
+                TPB_LAUNCH("col_kernel", (col_kernel<Acc, 1>), grid, 256, sm, st, in, pl.o_stride, pl.L, pl.l_stride, pl.I, pl.tiles, pl.tx_n, pl.lchunk, w, e, ov, oi);
             }
-            TPB_LAUNCH_OK("col_kernel");
             if (pl.S > 1) {
                 unsigned fg = (unsigned)ceil_div(pl.O * pl.I, 256);
-                col_finalize_kernel<Acc><<<fg, 256, 0, st>>>((const Packed*)ws, pl.O, pl.S, pl.I, (double)pl.count, e, ov, oi);
-                TPB_LAUNCH_OK("col_finalize_kernel");
+                TPB_LAUNCH("col_finalize_kernel", col_finalize_kernel<Acc>, dim3(fg), 256, 0, st, (const Packed*)ws, pl.O, pl.S, pl.I, (double)pl.count, e, ov, oi);
             }
             return TPB200_OK;
         }
         case ST_GENERIC: {
             unsigned grid = (unsigned)ceil_div(pl.gen.outs, 8);
-            generic_kernel<Acc><<<grid, 256, 0, st>>>(in, pl.gen, e, ov, oi);
-            TPB_LAUNCH_OK("generic_kernel");
+            TPB_LAUNCH("generic_kernel", generic_kernel<Acc>, dim3(grid), 256, 0, st, in, pl.gen, e, ov, oi);
             return TPB200_OK;
         }
     }
@@ -659,13 +654,13 @@ extern "C" int tpb200_reduce(int op, const void* in, int dtype, int ndim, const 
 // ---------------------------------------------------------------- sharded whole tensor ------
 namespace tpb {
 
-static void flat_plan(const void* in, int64_t n, Plan* pl) {
+static void flat_plan(const void* in, int64_t n, Family fam, Plan* pl) {
     const int sms = sm_count();
     RowGeom& g = pl->row;
     g.rows = 1; g.k1 = 1; g.ks0 = 0; g.ks1 = 0; g.nseg = 1; g.seglen = n; g.seg_stride = 0;
-    long long S = std::max(1LL, std::min((long long)sms * split_slices_per_sm(n, sms), (long long)(n / 16384)));
-    pl->chunk = round_up(ceil_div(std::max<long long>(n, 1), S), 4);
-    pl->S = (int)std::max(1LL, ceil_div((long long)n, pl->chunk));
+    long long S = std::max(1LL, std::min((long long)sms * split_ctas_per_sm(fam), (long long)(n / 16384)));
+    pl->chunk = kSplitBlock;
+    pl->S = (int)std::max(1LL, std::min(S, ceil_div(std::max<long long>(n, 1), pl->chunk)));
     pl->threads = 512;
     pl->outs = 1;
     pl->count = n;
@@ -677,20 +672,17 @@ static void flat_plan(const void* in, int64_t n, Plan* pl) {
 template <class Acc>
 static int launch_partial(const Plan& pl, const float* in, long long offset, Packed* out, void* ws,
                           cudaStream_t st) {
-    dim3 grid((unsigned)pl.S, 1);
-    row_split_kernel<Acc><<<grid, pl.threads, 0, st>>>(in, pl.row, pl.chunk, (Packed*)ws);
-    TPB_LAUNCH_OK("row_split_kernel");
+    TPB_LAUNCH("row_split_kernel", row_split_kernel<Acc>, dim3((unsigned)pl.S), pl.threads, 0, st, in, pl.row, pl.chunk, pl.S, (Packed*)ws);
     Epilogue e{0, 0};
-    finalize_kernel<Acc><<<1, 32, 0, st>>>((const Packed*)ws, 1, pl.S, (double)pl.count, e, nullptr, nullptr, out, offset);
-    TPB_LAUNCH_OK("finalize_kernel");
+    TPB_LAUNCH("finalize_kernel", finalize_kernel<Acc>, dim3(1), 32, 0, st, (const Packed*)ws, 1LL, pl.S, (double)pl.count, e, (float*)nullptr,
+               (long long*)nullptr, out, offset);
     return TPB200_OK;
 }
 
 template <class Acc>
 static int launch_combine(const Packed* parts, int n, double count, Epilogue e, float* ov,
                           long long* oi, cudaStream_t st) {
-    finalize_kernel<Acc><<<1, 32, 0, st>>>(parts, 1, n, count, e, ov, oi, nullptr, 0);
-    TPB_LAUNCH_OK("finalize_kernel");
+    TPB_LAUNCH("finalize_kernel", finalize_kernel<Acc>, dim3(1), 32, 0, st, parts, 1LL, n, count, e, ov, oi, (Packed*)nullptr, 0LL);
     return TPB200_OK;
 }
 
@@ -700,7 +692,7 @@ extern "C" size_t tpb200_reduce_partial_workspace_bytes(int family, int dtype, i
     (void)family;
     if (dtype != TPB200_F32 || n < 0) return 0;
     Plan pl;
-    flat_plan(nullptr, n, &pl);
+    flat_plan(nullptr, n, FAM_SUM, &pl);   // the size covers every family
     return pl.ws_bytes;
 }
 
@@ -716,7 +708,7 @@ extern "C" int tpb200_reduce_partial(int family, const void* in, int dtype, int6
     if (n > 0 && !in) return fail(TPB200_ERR_INVALID, "input pointer is NULL");
     if (((uintptr_t)partial_out) & 7) return fail(TPB200_ERR_INVALID, "partial_out must be 8-byte aligned");
     Plan pl;
-    flat_plan(in, n, &pl);
+    flat_plan(in, n, fam, &pl);
     int rc = check_ws(pl, workspace, workspace_bytes);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
@@ -809,8 +801,12 @@ extern "C" int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int6
     if (wants_val && !out_val) return fail(TPB200_ERR_INVALID, "out_val is NULL");
     if (wants_idx && !out_idx) return fail(TPB200_ERR_INVALID, "out_idx is NULL");
 
+    // the very plan tpb200_reduce makes for a contiguous 1-D tensor with every dim reduced, so the
+    // two entry points run the same kernels in the same geometry and agree bit for bit
     Plan pl;
-    flat_plan(in, n, &pl);
+    const int64_t sizes1[1] = {n}, strides1[1] = {1};
+    int prc = make_plan(in, 1, sizes1, strides1, 0, fam, &pl);
+    if (prc) return prc;
     if (pl.ws_bytes > (size_t)TPB200_NOALLOC_SCRATCH_BYTES)
         return fail(TPB200_ERR_UNSUPPORTED, "this device needs %zu bytes of scratch, the built-in array holds %d",
                     pl.ws_bytes, (int)TPB200_NOALLOC_SCRATCH_BYTES);
@@ -818,7 +814,7 @@ extern "C" int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int6
     int rc = noalloc_scratch_address(&scratch);
     if (rc) return rc;
 
-    // Pass 1 overwrites every record that pass 2 reads, so nothing left by an earlier call is used
+    // Short inputs need no scratch at all (one warp or one CTA reduces them).  Pass 1 overwrites every record that pass 2 reads, so nothing left by an earlier call is used
     // and nothing has to be cleared.
     Epilogue e{op, (long long)correction};
     float* ov = wants_val ? (float*)out_val : nullptr;
@@ -971,7 +967,7 @@ extern "C" int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, i
     if (wants_idx && !out_idx) return fail(TPB200_ERR_INVALID, "out_idx is NULL");
     if (n > 0 && !in) return fail(TPB200_ERR_INVALID, "input pointer is NULL");
     Plan pl;
-    flat_plan(in, n, &pl);
+    flat_plan(in, n, fam, &pl);
     int rc = check_ws(pl, workspace, workspace_bytes);
     if (rc) return rc;
     Epilogue e{op, (long long)correction};
@@ -984,10 +980,9 @@ extern "C" int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, i
     const int max_polls = g_exchange_polls.load(std::memory_order_relaxed);
 #define TPB_LAUNCH_X(ACC)                                                                                    \
     do {                                                                                                     \
-        row_split_kernel<ACC><<<dim3((unsigned)pl.S, 1), pl.threads, 0, st>>>(x, pl.row, pl.chunk, (Packed*)workspace); \
-        TPB_LAUNCH_OK("row_split_kernel");                                                                   \
-        finalize_exchange_kernel<ACC><<<1, 32, 0, st>>>((const Packed*)workspace, pl.S, (long long)global_offset, \
-            rank, world, peers, tc, e, ov, oi, status, max_polls);                                           \
+        TPB_LAUNCH("row_split_kernel", row_split_kernel<ACC>, dim3((unsigned)pl.S), pl.threads, 0, st, x, pl.row, pl.chunk, pl.S, (Packed*)workspace); \
+        TPB_LAUNCH("finalize_exchange_kernel", finalize_exchange_kernel<ACC>, dim3(1), 32, 0, st, (const Packed*)workspace, pl.S, \
+                   (long long)global_offset, rank, world, peers, tc, e, ov, oi, status, max_polls);          \
     } while (0)
     switch (fam) {
         case FAM_SUM: TPB_LAUNCH_X(SumAcc); break;
@@ -996,6 +991,5 @@ extern "C" int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, i
         case FAM_MIN: TPB_LAUNCH_X(ExtAcc<false>); break;
     }
 #undef TPB_LAUNCH_X
-    TPB_LAUNCH_OK("finalize_exchange_kernel");
     return TPB200_OK;
 }

@@ -165,16 +165,6 @@ __device__ __forceinline__ const float* topk_row(const float* in, const TopkGeom
     return in + a * g.ks0 + b * g.ks1;
 }
 
-// The scanning kernels below also serve as the second launch behind topk_select_kernel: `redo`
-// then holds one flag per row and only flagged rows are processed.  As a dependent launch the
-// kernel may have started before the first one finished: wait for it (a no-op otherwise).
-__device__ __forceinline__ bool row_wanted(const int* redo, long long r) {
-    if (redo == nullptr) return true;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    return *(const volatile int*)(redo + r) != 0;
-}
-
 // ------------------------------------------------------------------ streaming kernel -------
 // Every warp streams its own tiles (warp w of NW takes warp-tiles w, w+NW, ... of the slice) with plain
 // 128-bit streaming loads, eight per lane and iteration (1024 elements per warp-tile), exactly
@@ -354,22 +344,18 @@ enum { kActCut = 0, kActFinal = 1 };
 // Give-up codes left in the status word (low byte; the rendezvous round follows in the next bits).
 enum { kErrRendezvous = 2, kErrRetry = 3, kErrPolling = 4 };
 
+// The body of the rendezvous kernel: slice s of row r (row points at the row's first element), with
+// the candidate buffer buf (g.B words), the partition target buf2 (g.B / 2 words) and the control
+// block sh in the caller's shared memory.  Called by every thread of a CTA of NW warps.  It is the
+// whole of topk_stream_kernel, and topk_select_kernel calls it on the rows that fail its check.
 template <bool LARGEST, bool VEC, int NW>
-__global__ void __launch_bounds__(NW * 32, 32 / NW)
-topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
-                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status,
-                   const int* __restrict__ redo) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    unsigned long long* buf = reinterpret_cast<unsigned long long*>(smem_raw);
-    unsigned long long* buf2 = buf + g.B;   // B/2 words: target of the sample-select partition
-    __shared__ StreamShared sh;
+__device__ __forceinline__ void stream_body(const float* __restrict__ row, const TopkGeom& g, int s, long long r,
+                                            unsigned long long* buf, unsigned long long* buf2, StreamShared& sh,
+                                            unsigned long long* __restrict__ ws, float* __restrict__ out_val,
+                                            long long* __restrict__ out_idx, int* status) {
     constexpr int kStreamWarps = NW;
     constexpr int kStreamThreads = NW * 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int s = (int)(blockIdx.x % (unsigned)g.S);
-    const long long r = (long long)(blockIdx.x / (unsigned)g.S);
-    if (!row_wanted(redo, r)) return;
-    const float* row = topk_row(in, g, r);
     const long long begin = (long long)s * g.chunk;
     long long len = g.len - begin;
     if (len > g.chunk) len = g.chunk;
@@ -652,6 +638,27 @@ topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     }
 }
 
+// The same as a real function, for topk_select_kernel: the geometry travels by value, so the body
+// works on a private copy that no store can alias.
+template <bool LARGEST, bool VEC, int NW>
+__device__ __noinline__ void stream_body_call(const float* __restrict__ row, TopkGeom g, long long r,
+                                              unsigned long long* buf, StreamShared& sh, float* __restrict__ out_val,
+                                              long long* __restrict__ out_idx, int* status) {
+    stream_body<LARGEST, VEC, NW>(row, g, 0, r, buf, buf + g.B, sh, nullptr, out_val, out_idx, status);
+}
+
+template <bool LARGEST, bool VEC, int NW>
+__global__ void __launch_bounds__(NW * 32, 32 / NW)
+topk_stream_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
+                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned long long* buf = reinterpret_cast<unsigned long long*>(smem_raw);
+    __shared__ StreamShared sh;
+    const int s = (int)(blockIdx.x % (unsigned)g.S);
+    const long long r = (long long)(blockIdx.x / (unsigned)g.S);
+    stream_body<LARGEST, VEC, NW>(topk_row(in, g, r), g, s, r, buf, buf + g.B, sh, ws, out_val, out_idx, status);
+}
+
 // ------------------------------------------------------------------ small-k streaming kernel
 // k <= 64.  Same one-pass idea as topk_stream_kernel, but after the bootstrap NO barrier of the CTA
 // is left, candidates never go back to memory, and a cut never stops the other warps:
@@ -765,14 +772,12 @@ __device__ __noinline__ bool cut_chunk(unsigned long long* ring, SmallShared* sh
 template <bool LARGEST, bool VEC, int NW>
 __global__ void __launch_bounds__(NW * 32, NW == 4 ? 7 : (NW == 8 ? 4 : 2))
 topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long* __restrict__ ws,
-                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status,
-                   const int* __restrict__ redo) {
+                   float* __restrict__ out_val, long long* __restrict__ out_idx, int* status) {
     __shared__ __align__(16) unsigned long long ring[kRing];
     __shared__ SmallShared sh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int s = (int)(blockIdx.x % (unsigned)g.S);
     const long long r = (long long)(blockIdx.x / (unsigned)g.S);
-    if (!row_wanted(redo, r)) return;
     const float* row = topk_row(in, g, r);
     const long long begin = (long long)s * g.chunk;
     long long len = g.len - begin;
@@ -988,12 +993,10 @@ topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
 template <bool LARGEST, bool FROM_ROW>
 __global__ void __launch_bounds__(kSortThreads)
 topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long long* __restrict__ ws,
-                 int n_items, int N, float* __restrict__ out_val, long long* __restrict__ out_idx,
-                 const int* __restrict__ redo) {
+                 int n_items, int N, float* __restrict__ out_val, long long* __restrict__ out_idx) {
     extern __shared__ __align__(16) unsigned long long buf[];
     const int tid = threadIdx.x, nthr = blockDim.x;
     const long long r = blockIdx.x;
-    if (!row_wanted(redo, r)) return;
     const float* row = topk_row(in, g, r);
     if (FROM_ROW) {
         for (int i = tid; i < N; i += nthr)
@@ -1080,8 +1083,7 @@ struct TopkPlan {
     bool vec = false;
     int N = 0;            // sort size of the sort-row path
     int mergeN = 0;       // sort size of the slice merge (S > 1)
-    size_t ws_bytes = 0;  // whole workspace: redo flags of the select path first, slice survivors after
-    size_t redo_bytes = 0;
+    size_t ws_bytes = 0;  // slice survivors of the scanning kernels (S > 1); the select path needs none
     long long out_numel = 0;
     // select path (topk_select_kernel first, `path` as the second launch for flagged rows)
     bool select = false;
@@ -1155,8 +1157,15 @@ static bool plan_select(long long rows, long long len, long long k, int sms, Top
     sg.r = r;
     sg.cap = cap;
     sg.tpw = tpw;
+    sg.prefetch = 0;
+    env_int("TPB200_SEL_PREFETCH", &sg.prefetch);
+    sg.inplace = 0;
+    env_int("TPB200_SEL_INPLACE", &sg.inplace);
     sg.trigger = 1;
     sg.chunk = round_up(ceil_div(len, S), 4);
+    // geometry of the scan that redoes a row inside the kernel (the rendezvous kernel's, one slice)
+    sg.fb_B = pow2_ceil(std::max<long long>(4 * k, 1024));
+    sg.fb_soft = (int)std::min<long long>(sg.fb_B / 2, std::max<long long>(320, 3 * k));
     pl->sel_warps = nw;
     return true;
 }
@@ -1229,14 +1238,11 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     // rows ride on grid.x together with the slices: 2^31 - 1 CTAs per launch
     auto grid_ok = [&](long long S) { return rows <= 0x7fffffffLL / std::max(1LL, S); };
     auto finish = [&]() {
+        pl->select = plan_select(rows, len, k, sms, pl);
+        if (pl->select) return TPB200_OK;       // one kernel, no scratch
         if (g.S > 1) {
             pl->mergeN = std::max(2, pow2_ceil((long long)g.S * k));
             pl->ws_bytes = (size_t)rows * g.S * k * sizeof(unsigned long long);
-        }
-        pl->select = plan_select(rows, len, k, sms, pl);
-        if (pl->select) {
-            pl->redo_bytes = (size_t)round_up(rows * (long long)sizeof(int), 256);
-            pl->ws_bytes += pl->redo_bytes;
         }
         return TPB200_OK;
     };
@@ -1311,56 +1317,21 @@ static int allow_smem(K kernel, size_t bytes) {
     return TPB200_OK;
 }
 
-// One launch through cudaLaunchKernelEx: `cluster` > 1 makes clusters of that many CTAs along x,
-// `dependent` lets the kernel start before the previous kernel of the stream has finished (it must
-// then call griddepcontrol.wait before it touches memory: row_wanted() does).
-template <class... KArgs, class... Args>
-static cudaError_t launch_ex(void (*kernel)(KArgs...), unsigned grid, int threads, size_t smem, cudaStream_t st,
-                             int cluster, bool dependent, Args... args) {
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3((unsigned)threads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    unsigned na = 0;
-    if (cluster > 1) {
-        attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = (unsigned)cluster;
-        attr[na].val.clusterDim.y = 1;
-        attr[na].val.clusterDim.z = 1;
-        ++na;
-    }
-    if (dependent) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
-
-static bool dependent_launch_on() {
-    int v = 1;
-    env_int("TPB200_PDL", &v);
-    return v != 0;
-}
-
 template <bool LARGEST>
-static int select_launch(const TopkPlan& pl, const float* in, float* ov, long long* oi, int* redo, cudaStream_t st) {
+static int select_launch(const TopkPlan& pl, const float* in, float* ov, long long* oi, cudaStream_t st) {
     const TopkGeom& g = pl.g;
     SelGeom sg = pl.sel;
     sg.trigger = dependent_launch_on() ? 1 : 0;
-    const size_t sm = (size_t)sg.cap * 8;
+    const size_t sm = std::max((size_t)sg.cap * 8, (size_t)sg.fb_B * 12);
     const unsigned grid = (unsigned)(g.rows * sg.S);
     const int nw = pl.sel_warps;
+    int* status = device_status_word();
     cudaError_t e = cudaSuccess;
 #define TPB_LAUNCH_SELECT(V, W)                                                                           \
     do {                                                                                                  \
         int rc = allow_smem(topk_select_kernel<LARGEST, V, W>, sm);                                       \
         if (rc) return rc;                                                                                \
-        e = launch_ex(topk_select_kernel<LARGEST, V, W>, grid, W * 32, sm, st, sg.S, sg.trigger != 0, in, g, sg, ov, oi, redo); \
+        e = launch_ex(topk_select_kernel<LARGEST, V, W>, dim3(grid), W * 32, sm, st, sg.S, sg.trigger != 0, in, g, sg, ov, oi, status); \
     } while (0)
     if (pl.vec) { if (nw == 16) TPB_LAUNCH_SELECT(true, 16); else if (nw == 8) TPB_LAUNCH_SELECT(true, 8); else TPB_LAUNCH_SELECT(true, 4); }
     else        { if (nw == 16) TPB_LAUNCH_SELECT(false, 16); else if (nw == 8) TPB_LAUNCH_SELECT(false, 8); else TPB_LAUNCH_SELECT(false, 4); }
@@ -1379,27 +1350,20 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
         if (rc) return rc;
         int threads = std::min(kSortThreads, std::max(32, pl.N / 2));
         if (g.rows > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
-        topk_sort_kernel<LARGEST, true><<<(unsigned)g.rows, threads, sm, st>>>(in, g, nullptr, (int)g.len, pl.N, ov, oi, nullptr);
-        TPB_LAUNCH_OK("topk_sort_kernel");
+        TPB_LAUNCH("topk_sort_kernel", (topk_sort_kernel<LARGEST, true>), dim3((unsigned)g.rows), threads, sm, st, in, g,
+                   (const unsigned long long*)nullptr, (int)g.len, pl.N, ov, oi);
         return TPB200_OK;
     }
-    // select path: the sampled-threshold kernel first; the scanning kernels below then redo only
-    // the rows it flagged (as a dependent launch: their CTAs are resident when the first kernel ends)
-    int* redo = nullptr;
-    if (pl.select) {
-        redo = (int*)ws;
-        ws = (unsigned char*)ws + pl.redo_bytes;
-        int rc = select_launch<LARGEST>(pl, in, ov, oi, redo, st);
-        if (rc) return rc;
-    }
-    const bool dep = redo != nullptr && dependent_launch_on();
+    // long rows: the sampled-threshold kernel, which redoes the rows that fail its check itself
+    if (pl.select) return select_launch<LARGEST>(pl, in, ov, oi, st);
+    const bool dep = false;   // the scanning kernels launch the ordinary way
     const unsigned grid = (unsigned)(g.rows * g.S);
     unsigned long long* w = g.S > 1 ? (unsigned long long*)ws : nullptr;
     int* status = device_status_word();
     const int threads = g.warps * 32;
     cudaError_t e = cudaSuccess;
     if (pl.path == TK_SMALLK) {
-#define TPB_LAUNCH_SMALLK(V, W) e = launch_ex(topk_smallk_kernel<LARGEST, V, W>, grid, threads, 0, st, 1, dep, in, g, w, ov, oi, status, (const int*)redo)
+#define TPB_LAUNCH_SMALLK(V, W) e = launch_ex(topk_smallk_kernel<LARGEST, V, W>, dim3(grid), threads, 0, st, 1, dep, in, g, w, ov, oi, status)
         if (pl.vec) {
             if (g.warps == 16) TPB_LAUNCH_SMALLK(true, 16); else if (g.warps == 8) TPB_LAUNCH_SMALLK(true, 8); else TPB_LAUNCH_SMALLK(true, 4);
         } else {
@@ -1413,7 +1377,7 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
     do {                                                                                                 \
         int rc = allow_smem(topk_stream_kernel<LARGEST, V, W>, sm);                                      \
         if (rc) return rc;                                                                               \
-        e = launch_ex(topk_stream_kernel<LARGEST, V, W>, grid, threads, sm, st, 1, dep, in, g, w, ov, oi, status, (const int*)redo); \
+        e = launch_ex(topk_stream_kernel<LARGEST, V, W>, dim3(grid), threads, sm, st, 1, dep, in, g, w, ov, oi, status); \
     } while (0)
         if (pl.vec) { if (g.warps == 16) TPB_LAUNCH_STREAM(true, 16); else TPB_LAUNCH_STREAM(true, 8); }
         else        { if (g.warps == 16) TPB_LAUNCH_STREAM(false, 16); else TPB_LAUNCH_STREAM(false, 8); }
@@ -1425,8 +1389,8 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
         int rc = allow_smem(topk_sort_kernel<LARGEST, false>, msm);
         if (rc) return rc;
         int mthreads = std::min(kSortThreads, std::max(32, pl.mergeN / 2));
-        e = launch_ex(topk_sort_kernel<LARGEST, false>, (unsigned)g.rows, mthreads, msm, st, 1, dep, in, g, (const unsigned long long*)w,
-                      g.S * (int)g.k, pl.mergeN, ov, oi, (const int*)redo);
+        e = launch_ex(topk_sort_kernel<LARGEST, false>, dim3((unsigned)g.rows), mthreads, msm, st, 1, dep, in, g, (const unsigned long long*)w,
+                      g.S * (int)g.k, pl.mergeN, ov, oi);
         if (e != cudaSuccess) return cuda_fail(e, "topk_sort_kernel(merge)");
     }
     return TPB200_OK;
@@ -1463,10 +1427,11 @@ extern "C" int tpb200_topk_plan_info(int dtype, int ndim, const int64_t* sizes, 
     int rc = topk_plan((const void*)16, ndim, sizes, strides, dim, k, &pl);
     if (rc) return rc;
     const int scan_launches = pl.path == TK_NONE ? 0 : 1 + (pl.path != TK_SORTROW && pl.g.S > 1 ? 1 : 0);
+    const int launches = pl.select ? 1 : scan_launches;
     const int64_t v[TPB200_PLAN_INFO_FIELDS] = {
         (int64_t)pl.path, pl.g.S, pl.g.warps, pl.select ? 1 : 0, pl.select ? pl.sel.S : 0,
         pl.select ? pl.sel_warps : 0, pl.select ? pl.sel.r : 0, pl.select ? pl.sel.cap : 0, pl.select ? pl.sel.tpw : 0,
-        scan_launches + (pl.select ? 1 : 0), (int64_t)pl.ws_bytes};
+        launches, (int64_t)pl.ws_bytes};
     for (int i = 0; i < n_info && i < TPB200_PLAN_INFO_FIELDS; ++i) info[i] = v[i];
     return TPB200_OK;
 }

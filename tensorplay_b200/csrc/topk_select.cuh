@@ -32,11 +32,11 @@
 //   4. verify     the first CTA cuts the candidates to the k best, sorted.  The result is exact iff
 //                 no buffer overflowed and the k-th best candidate has a key of at least T*: then at
 //                 least k elements reach T*, all of them are candidates, and everything that is not a
-//                 candidate ranks below them.  Otherwise the row is flagged and a second launch -- the
-//                 scanning kernels of topk.cu, which need no assumption -- redoes exactly the flagged
-//                 rows.  Rows whose beginning says nothing about the rest (sorted rows, all-equal rows,
-//                 rows with fewer than k numbers) go that way; they cost a second pass, never a wrong
-//                 answer.
+//                 candidate ranks below them.  Otherwise the same CTA scans the row again the way
+//                 topk_stream_kernel does (stream_body: a threshold learnt from cuts, no assumption).
+//                 Rows whose beginning says nothing about the rest (sorted rows, all-equal rows, rows
+//                 with fewer than k numbers) go that way; they cost a second pass, never a wrong
+//                 answer, and no second launch.
 //
 // Splitting a row is cheap here (the threshold does not depend on the scan), so the planner picks
 // CTA width and CTAs per row such that ONE wave of equal CTAs fills the GPU: co-resident CTAs share
@@ -71,12 +71,19 @@ struct SelGeom {
     int r;           // 1-based rank of the threshold key among a CTA's lane maxima
     int cap;         // candidate words of a CTA's buffer; also the limit per row
     int tpw;         // sample tiles per warp
-    int trigger;     // 1: let a dependent launch start early (programmatic dependent launch)
+    int prefetch;    // 1: hint the tiles after the first into L2 while the first is loaded
+    int inplace;     // 1: the final cut always compacts in place (exercises that path; slower)
+    int trigger;     // 1: launched as a dependent launch (programmatic dependent launch)
+    int fb_B, fb_soft;  // buffer words and first-cut fill of the scan that redoes a failed row
     long long chunk; // slice length
 };
 
 struct SelShared {
-    unsigned long long samp[128];   // pivot sample of the final cut
+    unsigned long long samp[128];   // pivot sample of the final cut, sorted descending
+    unsigned long long raw[128];    // the same before sorting
+    int wsum[32];                   // per-warp counts of the final cut's scan
+    int hist[130], fill[130], start[130];   // sample sort of the final cut: bucket sizes, fill marks, first positions
+    int bstar, taken;               // bucket of the k-th word; words in the buckets up to it
     unsigned bootk[kSelKeys];       // the warps' best lane maxima, as keys
     unsigned skeys[kSelKeys];       // the same, sorted descending
     unsigned tmax;                  // first CTA: largest threshold key reported by the other CTAs
@@ -86,18 +93,21 @@ struct SelShared {
     int bad;                        // first CTA: a CTA of the row had no threshold or overflowed
     int base;                       // this CTA's reservation in the first CTA's buffer
     int tmp;
+    StreamShared fb;                // control block of the scan that redoes a failed row
 };
 
 // The first CTA's last step: cut the n candidates in cand[0..n) to the k best, sorted, verify the
 // k-th against the row's threshold key `tstar`, write the row.  Called by every thread of the CTA;
 // returns true when the row must be redone.
 //   n <= 256              every candidate counts the candidates above it: its rank is its output slot
-//   n within 2x of k      CTA-wide bitonic sort of the padded buffer
-//   otherwise             a pivot from a sorted sample of 128 candidates is tried until between k and
-//                         two sort blocks of candidates reach it; those are compacted to the front
-//                         in place and sorted
+//   otherwise             sample sort: 128 sorted sample words split the candidates into 129 buckets;
+//                         the buckets that hold the k best are scattered behind the candidates and every
+//                         word's rank inside its bucket gives its output slot (measured on 2900
+//                         candidates, k = 1024: a 2048-word bitonic sort alone took 9 us of a 15 us cut)
+//   no room for that      a pivot from the sample is tried until between k and two sort blocks of
+//                         candidates reach it; those are compacted and sorted with the bitonic network
 template <bool LARGEST, int NT>
-__device__ bool sel_final(unsigned long long* cand, int n, int k, int cap, unsigned tstar, SelShared& sh,
+__device__ bool sel_final(unsigned long long* cand, int n, int k, int cap, unsigned tstar, bool inplace, SelShared& sh,
                           const float* row, long long es, float* ov, long long* oi) {
     const int tid = threadIdx.x, lane = tid & 31;
     auto emit = [&](int j, unsigned long long w) {
@@ -130,42 +140,138 @@ __device__ bool sel_final(unsigned long long* cand, int n, int k, int cap, unsig
         __syncthreads();
         return sh.tmp != 0;
     }
-    const int Nk = pow2_ceil_dev(k);
-    int m = n;
-    if (!(pow2_ceil_dev(n) <= 2 * Nk && pow2_ceil_dev(n) <= cap)) {
-        // pivot from a sorted sample
+    // ---- a sorted sample of 128 words (splitters), rank-sorted by P threads per word
+    {
+        constexpr int P = NT >= 512 ? 4 : (NT >= 256 ? 2 : 1);
+        if (tid < 128) sh.raw[tid] = cand[(long long)tid * n / 128];
+        __syncthreads();
+        const int i = tid / P, part = tid % P;
+        if (i < 128) {
+            const unsigned long long my = sh.raw[i];
+            int pos = 0;
+#pragma unroll 8
+            for (int j = part * (128 / P); j < (part + 1) * (128 / P); ++j) pos += sh.raw[j] > my ? 1 : 0;
+            if (P >= 2) pos += __shfl_xor_sync(kFull, pos, 1);
+            if (P >= 4) pos += __shfl_xor_sync(kFull, pos, 2);
+            if (part == 0) sh.samp[pos] = my;    // the words of a row are distinct: no two share a rank
+        }
+        for (int j = tid; j < 130; j += NT) { sh.hist[j] = 0; sh.fill[j] = 0; }
+        __syncthreads();
+    }
+    TPB_STAMP(10);
+    // ---- sample sort of the words that can reach the output.  Bucket of a word = number of
+    // splitters above it (0 .. 128); buckets are walked from the best down until they hold k words;
+    // those words are scattered bucket by bucket behind the candidates, and a word's rank inside its
+    // bucket (a scan of some twenty words) then gives its final position: it is written straight to
+    // the output.  No sort network at all.
+    auto bucket_of = [&](unsigned long long w) -> int {
+        int lo = 0, hi = 128;
+#pragma unroll
+        for (int step = 0; step < 7; ++step) { const int mid = (lo + hi) >> 1; if (sh.samp[mid] > w) lo = mid + 1; else hi = mid; }
+        return lo;
+    };
+    if (!inplace) {
+        for (int i = tid; i < n; i += NT) atomicAdd(&sh.hist[bucket_of(cand[i])], 1);
+        __syncthreads();
         if (tid < 32) {
-            unsigned long long v[4];
+            // exclusive prefix over the 129 buckets (five per lane) and the bucket in which the k-th word lies
+            int h[5], sum = 0;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) v[e] = cand[(long long)(tid * 4 + e) * n / 128];
-            warp_sort_desc<4>(v, tid);
+            for (int e = 0; e < 5; ++e) { const int bb = tid * 5 + e; h[e] = bb < 129 ? sh.hist[bb] : 0; sum += h[e]; }
+            int incl = sum;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) sh.samp[tid * 4 + e] = v[e];
+            for (int d = 1; d < 32; d <<= 1) { const int t = __shfl_up_sync(kFull, incl, d); if (tid >= d) incl += t; }
+            int run = incl - sum;
+#pragma unroll
+            for (int e = 0; e < 5; ++e) {
+                const int bb = tid * 5 + e;
+                if (bb < 129) {
+                    sh.start[bb] = run;
+                    if (run < k && run + h[e] >= k) { sh.bstar = bb; sh.taken = run + h[e]; }
+                }
+                run += h[e];
+            }
         }
         __syncthreads();
+        const int bstar = sh.bstar, T = sh.taken;
+        TPB_STAMP(11);
+        if (n + T <= cap) {
+            unsigned long long* tmp = cand + n;
+            for (int i = tid; i < n; i += NT) {
+                const unsigned long long w = cand[i];
+                const int bb = bucket_of(w);
+                if (bb <= bstar) tmp[sh.start[bb] + atomicAdd(&sh.fill[bb], 1)] = w;
+            }
+            __syncthreads();
+            TPB_STAMP(12);
+            TPB_NOTE(14, T);
+            for (int p = tid; p < T; p += NT) {
+                const unsigned long long w = tmp[p];
+                const int bb = bucket_of(w);
+                const int s0 = sh.start[bb], s1 = s0 + sh.hist[bb];
+                int pos = s0;
+                for (int q = s0; q < s1; ++q) pos += tmp[q] > w ? 1 : 0;
+                if (pos < k) {
+                    if (pos == k - 1 && (unsigned)(w >> 32) < tstar) sh.tmp = 1;
+                    emit(pos, w);
+                }
+            }
+            __syncthreads();
+            TPB_STAMP(13);
+            return sh.tmp != 0;
+        }
+        // the bucket of the k-th word is too large for the room behind the candidates (or the buffer is
+        // nearly full): fall through to the pivot cut below, which works in place
+    }
+    const int Nk = pow2_ceil_dev(k);
+    int m = n;
+    unsigned long long* arr = cand;       // where the words to sort end up
+    if (!(pow2_ceil_dev(n) <= 2 * Nk && pow2_ceil_dev(n) <= cap)) {
         const int most = 2 * Nk < cap ? 2 * Nk : cap;
         // sample rank whose pivot is expected to keep about 1.19 k + 24 words
         int q = (int)(((long long)128 * (k + (k >> 3) + (k >> 4) + 24) + n - 1) / n) + 1;
         bool ok = false;
         unsigned long long pivot = 0ull;
+        int excl = 0;
         for (int attempt = 0; attempt < 4 && q <= 127; ++attempt, q += 6) {
             pivot = sh.samp[q];
-            int cnt = 0;
-            for (int i = tid; i < n; i += NT) cnt += cand[i] >= pivot ? 1 : 0;
-            cnt = __reduce_add_sync(kFull, cnt);
-            if (lane == 0 && cnt) atomicAdd(&sh.tmp, cnt);
+            // thread t counts over the words t, t + NT, ...; an exclusive scan of the counts gives
+            // every thread the place of its words among those that are kept
+            int c = 0;
+            for (int i = tid; i < n; i += NT) c += cand[i] >= pivot ? 1 : 0;
+            int incl = c;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_up_sync(kFull, incl, d);
+                if (lane >= d) incl += t;
+            }
+            if (lane == 31) sh.wsum[tid >> 5] = incl;
             __syncthreads();
-            const int total = sh.tmp;
+            int woff = 0, total = 0;
+#pragma unroll
+            for (int w = 0; w < NT / 32; ++w) {
+                const int v = sh.wsum[w];
+                woff += w < (tid >> 5) ? v : 0;
+                total += v;
+            }
             __syncthreads();
-            if (tid == 0) sh.tmp = 0;
-            __syncthreads();
+            excl = woff + incl - c;
             if (total >= k && total <= most) { ok = true; m = total; break; }
         }
+        TPB_STAMP(11);
         if (!ok) {
             if (pow2_ceil_dev(n) > cap) return true;   // no pivot fits and no room to sort everything: redo
+        } else if (n + most <= cap) {
+            // room behind the candidates: every thread copies its kept words to its place there
+            arr = cand + n;
+            for (int i = tid; i < n; i += NT) {
+                const unsigned long long w = cand[i];
+                if (w >= pivot) arr[excl++] = w;
+            }
+            __syncthreads();
         } else {
-            // compact the words >= pivot to the front, in place: a word only ever moves to a lower
-            // position, and a batch is read completely before any of it is written
+            // no room: compact to the front in place.  A word only ever moves to a lower position, and
+            // a batch is read completely before any of it is written
             for (int base = 0; base < n; base += NT) {
                 const int i = base + tid;
                 const unsigned long long w = i < n ? cand[i] : 0ull;
@@ -181,18 +287,21 @@ __device__ bool sel_final(unsigned long long* cand, int n, int k, int cap, unsig
         }
     }
     const int N = pow2_ceil_dev(m) < 2 ? 2 : pow2_ceil_dev(m);
-    for (int i = m + tid; i < N; i += NT) cand[i] = 0ull;
+    for (int i = m + tid; i < N; i += NT) arr[i] = 0ull;
     __syncthreads();
-    bitonic_desc(cand, N, tid, NT);
-    if ((unsigned)(cand[k - 1] >> 32) < tstar) return true;
-    for (int j = tid; j < k; j += NT) emit(j, cand[j]);
+    TPB_STAMP(12);
+    TPB_NOTE(14, m);
+    bitonic_desc(arr, N, tid, NT);
+    TPB_STAMP(13);
+    if ((unsigned)(arr[k - 1] >> 32) < tstar) return true;
+    for (int j = tid; j < k; j += NT) emit(j, arr[j]);
     return false;
 }
 
 template <bool LARGEST, bool VEC, int NW>
 __global__ void __launch_bounds__(NW * 32, NW == 4 ? 7 : (NW == 8 ? 4 : 2))
 topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* __restrict__ out_val,
-                   long long* __restrict__ out_idx, int* __restrict__ redo) {
+                   long long* __restrict__ out_idx, int* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned long long* cand = reinterpret_cast<unsigned long long*>(smem_raw);   // cap words
     __shared__ SelShared sh;
@@ -217,10 +326,13 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
     // see it initialised.  Arrive at the cluster barrier now (the release orders the line above) and
     // wait for it only after the scan, when every CTA has long arrived: the barrier costs nothing.
     if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    if (sg.trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // as a dependent launch this kernel may have started before the previous kernel of the stream
-    // has finished: nothing is read or written before this point
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (sg.trigger) {
+        // launched as a dependent launch (an experiment switch, off by default): this kernel may have
+        // started before the previous kernel of the stream has finished; nothing is read or written
+        // before this point
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
 
     auto elem_off = [&](long long off, int j) -> long long { return off + ((j >> 2) * 32 + lane) * 4 + (j & 3); };
     // A tile in registers; elements past the end of the slice read as NaN (never a candidate).
@@ -273,6 +385,14 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
     float mx = NAN;   // fmaxf / fminf ignore a NaN operand
     for (int t = 0; t < sg.tpw; ++t) {
         load_tile(v, (long long)(t * NW + warp) * kWarpTile);
+        if (VEC && sg.prefetch && t == 0) {
+            // this warp's later sample tiles and its first scan tile: asked into L2 behind the loads of
+            // the first tile, so that the loads that follow one another below find them there
+            for (int u = 1; u <= sg.tpw; ++u) {
+                const long long o = (long long)(u * NW + warp) * kWarpTile;
+                if (o + kWarpTile <= len) asm volatile("prefetch.global.L2 [%0];" ::"l"(slice + o + lane * 32));
+            }
+        }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             if (LARGEST) mx = fmaxf(fmaxf(mx, v[u].x), fmaxf(fmaxf(v[u].y, v[u].z), v[u].w));
@@ -387,9 +507,21 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
     bad = bad || n < k;
     TPB_NOTE(9, n);
     TPB_STAMP(5);
-    if (!bad) bad = sel_final<LARGEST, NT>(cand, n, k, cap, tstar, sh, row, g.es, out_val + r * k, out_idx + r * k);
-    if (tid == 0) redo[r] = bad ? 1 : 0;
+    if (!bad) bad = sel_final<LARGEST, NT>(cand, n, k, cap, tstar, sg.inplace != 0, sh, row, g.es, out_val + r * k, out_idx + r * k);
     TPB_STAMP(7);
+    if (bad) {
+        // The check failed (or a buffer overflowed, or the sample held too few numbers): this CTA scans
+        // the whole row again the way topk_stream_kernel does, with a threshold that is learnt from
+        // cuts and needs no assumption.  The other CTAs of the row have left.
+        __syncthreads();
+        TopkGeom fg = g;
+        fg.S = 1;
+        fg.chunk = g.len;
+        fg.B = sg.fb_B;
+        fg.soft = sg.fb_soft;
+        fg.warps = NW;
+        stream_body_call<LARGEST, VEC, NW>(row, fg, r, cand, sh.fb, out_val, out_idx, status);
+    }
 }
 
 }  // namespace tpb

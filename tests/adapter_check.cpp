@@ -147,7 +147,7 @@ int main() {
                 std::memcmp(hv0.data(), wv0.data(), wv0.size() * 4) != 0 || hi0 != wi0) { printf("FAIL topk(dim=0, largest=%d)\n", largest); ++fails; }
         }
         auto [v1, i1] = Tensor::topk(gt2, 1, 1, true, true);                  // function variant; k = 1 is argmax
-        equal_i("topk(k=1) indices == argmax", i1.reshape({R}), ct2.argmax(std::optional<int64_t>(1), false));
+        equal_i("topk(k=1) indices == argmax", i1, ct2.argmax(std::optional<int64_t>(1), false));   // [R,1] against [R]: same elements
         try { gt2.topk(C + 1, -1, true, true); printf("FAIL: no error for k > len\n"); ++fails; }
         catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "selected index k out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }
     }

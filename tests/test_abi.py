@@ -60,7 +60,7 @@ def test_argument_checks_need_no_gpu(lib):
     assert lib.tpb200_reduce_partial(0, None, 0, -1, 0, None, None, 0, None) == _lib.ERR_INVALID
 
 
-def test_workspace_planner(lib):
+def test_workspace_planner(lib, monkeypatch):
     from tensorplay_b200 import _lib
     i64 = _lib.i64_array
     P = _lib.PARTIAL_BYTES
@@ -73,11 +73,16 @@ def test_workspace_planner(lib):
     # column reduction over dim 1 of [64, 4096, 512]: records for [64, S, 512]
     n = lib.tpb200_reduce_workspace_bytes(0, 0, 3, i64([64, 4096, 512]), i64([4096 * 512, 512, 1]), 1 << 1)
     assert n % (64 * 512 * P) == 0
-    # top-k: one slice per row needs no scratch; several slices need S*k words per row (the select
-    # path adds one redo flag per row in front, rounded up to 256 bytes)
+    # top-k: short rows and the sampled-threshold kernel need no scratch; the scanning kernels alone
+    # need S*k words per row when they split rows into slices
     assert lib.tpb200_topk_workspace_bytes(0, 2, i64([4, 1000]), i64([1000, 1]), 1, 5) == 0
+    assert lib.tpb200_topk_workspace_bytes(0, 2, i64([8, 1 << 22]), i64([1 << 22, 1]), 1, 64) == 0
+    assert _lib.topk_plan_info([8, 1 << 22], [1 << 22, 1], 1, 64)["launches"] == 1
+    monkeypatch.setenv("TPB200_TOPK_SELECT", "0")
     n = lib.tpb200_topk_workspace_bytes(0, 2, i64([8, 1 << 22]), i64([1 << 22, 1]), 1, 64)
-    assert n > 256 and (n - 256) % (8 * 64 * 8) == 0
+    assert n > 0 and n % (8 * 64 * 8) == 0
+    assert _lib.topk_plan_info([8, 1 << 22], [1 << 22, 1], 1, 64)["launches"] == 2
+    monkeypatch.delenv("TPB200_TOPK_SELECT")
     # too small a workspace is refused before any launch
     rc = lib.tpb200_reduce(0, ctypes.c_void_p(16), 0, 1, i64([1 << 31]), i64([1]), 0, -1, 1,
                            ctypes.c_void_p(16), None, ctypes.c_void_p(256), 8, None)

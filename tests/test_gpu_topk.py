@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(params=["select", "scan"], autouse=True)
 def topk_path(request, monkeypatch):
-    """Every test runs twice: with the sampled-threshold kernel in front (the default for long rows;
-    the scanning kernels then only redo the rows it flags) and with the scanning kernels alone."""
+    """Every test runs twice: with the sampled-threshold kernel (the default for long rows; it redoes
+    the rows that fail its check with the scanning kernel's body) and with the scanning kernels alone."""
     monkeypatch.setenv("TPB200_TOPK_SELECT", "1" if request.param == "select" else "0")
     return request.param
 
@@ -194,8 +194,8 @@ def test_errors(cuda):
 @pytest.mark.parametrize("warps,slices", [("16", "1"), ("16", "2"), ("8", "4"), ("4", "8"), ("8", "1")])
 def test_select_kernel_geometries(cuda, warps, slices, monkeypatch, topk_path):
     """The sampled-threshold kernel with one CTA per row and with clusters of 2, 4 and 8 CTAs per row
-    (candidates merged through distributed shared memory), on rows it can finish itself and on rows
-    it must hand to the second launch: ascending rows (the sample says nothing about the rest),
+    (candidates merged through distributed shared memory), on rows that pass its check and on rows
+    it has to scan a second time: ascending rows (the sample says nothing about the rest),
     all-equal rows (every element is a candidate) and rows with fewer numbers than k."""
     if topk_path != "select":
         pytest.skip("select path only")
@@ -220,10 +220,10 @@ def test_select_kernel_geometries(cuda, warps, slices, monkeypatch, topk_path):
 
 
 @pytest.mark.parametrize("rank,pdl", [("1", "1"), ("1", "0"), ("90", "1")])
-def test_select_rows_redone_by_second_launch(cuda, rank, pdl, monkeypatch, topk_path):
+def test_select_rows_redone(cuda, rank, pdl, monkeypatch, topk_path):
     """A threshold taken too high (rank 1: the sample's maximum) leaves fewer than k candidates in
-    every row, one taken too low overflows the candidate buffer: either way the row is flagged and the
-    second launch produces it -- as a dependent launch and as an ordinary one."""
+    every row, one taken too low overflows the candidate buffer: either way the check fails and the
+    CTA scans the row again -- launched as a dependent launch and as an ordinary one."""
     if topk_path != "select":
         pytest.skip("select path only")
     from tensorplay_b200 import _lib
@@ -238,15 +238,15 @@ def test_select_rows_redone_by_second_launch(cuda, rank, pdl, monkeypatch, topk_
 
 
 def test_select_many_calls_in_one_graph(cuda, topk_path):
-    """Several calls captured in one CUDA graph (cluster launches and the dependent second launch as
-    graph nodes) give the same bits as eager calls."""
+    """Several calls captured in one CUDA graph (cluster launches, each a dependent launch of the one
+    before) give the same bits as eager calls."""
     if topk_path != "select":
         pytest.skip("select path only")
     import torch
     import tensorplay_b200 as tpb
     rng = np.random.default_rng(43)
     xs = [torch.from_numpy(rng.standard_normal((16, 150000)).astype(np.float32)).to(cuda) for _ in range(3)]
-    xs[1][3] = torch.sort(xs[1][3]).values          # one row of one input goes through the second launch
+    xs[1][3] = torch.sort(xs[1][3]).values          # one row of one input fails the check and is scanned again
     eager = [tpb.topk(x, 50) for x in xs]
     outs = [(torch.empty(16, 50, device=cuda), torch.empty(16, 50, dtype=torch.int64, device=cuda)) for _ in xs]
     stream = torch.cuda.Stream()

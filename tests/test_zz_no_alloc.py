@@ -60,6 +60,17 @@ def test_noalloc_matches_workspace_entry_point_on_two_calls_in_a_row(cuda):
         for op in OPS:
             got, want = _both(lib, _lib, torch, x, op)
             assert got == want, (op, x.numel(), got, want)
+    # short inputs, where one warp or one CTA does the whole reduction and the scratch array is not
+    # touched at all: still the same bits as the ordinary entry point
+    for m in (1, 1000, 20000, 40000):
+        xs = torch.from_numpy(rng.standard_normal(m).astype(np.float32)).to(cuda)
+        for op in OPS:
+            got, want = _both(lib, _lib, torch, xs, op)
+            assert got == want, (op, m, got, want)
+    empty = torch.empty(0, device=cuda)
+    for op in ("sum", "mean", "var"):
+        got, want = _both(lib, _lib, torch, empty, op)
+        assert got == want, (op, 0, got, want)
     # and the values are right, not merely equal to each other
     st = torch.cuda.current_stream().cuda_stream
     ov = torch.empty(1, device=cuda)
