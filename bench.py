@@ -228,6 +228,8 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
         b = 256 * 151936 * 4 + 256 * 50 * 12
         launches = tpb._lib.topk_plan_info([256, 151936], [151936, 1], 1, 50)["launches"]
         cases.append(Case("topk k=50 [256,151936]", lambda i: tpb.topk(xs[i % n], 50, -1, True, True, out=(ov, oi)), b, 256, launches, xs))
+        osm = torch.empty(256, 151936, device=dev)
+        cases.append(Case("softmax dim=-1 [256,151936]", lambda i: tpb.softmax(xs[i % n], -1, out=osm), 2 * 256 * 151936 * 4, 256, 1, xs))
     elif workload == "c1":
         n = copies_to_exceed_l2(4096 * 4096 * 4)
         xs = [gen_c1(torch, dev, gen) for _ in range(n)]
@@ -246,6 +248,13 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
                              ("norm p=2", lambda i: tpb.norm(xs[i % n], 2.0, -1, out=ov), 16384),
                              ("all", lambda i: tpb.all(xs[i % n], -1, out=ob), 4096)]:
             cases.append(Case(f"{op} dim=-1 [4096,4096]", fn, inb + outb, 4096, 1, xs))
+        # one step downstream of the row reductions: softmax / log_softmax read the input and write a
+        # result of the same size (algorithmic bytes = 2 x input); median reads it (three sweeps)
+        osm = torch.empty(4096, 4096, device=dev)
+        omed = torch.empty((), device=dev)
+        cases.append(Case("softmax dim=-1 [4096,4096]", lambda i: tpb.softmax(xs[i % n], -1, out=osm), 2 * inb, 4096, 1, xs))
+        cases.append(Case("log_softmax dim=-1 [4096,4096]", lambda i: tpb.log_softmax(xs[i % n], -1, out=osm), 2 * inb, 4096, 1, xs))
+        cases.append(Case("median [4096,4096]", lambda i: tpb.median(xs[i % n], out=omed), inb + 4, 1, 7, xs))
         # the same input every step: 64 MiB stays in the 126 MB L2.  Reported beside the cold figures,
         # never used for a roofline fraction.
         cases.append(Case("sum dim=-1 [4096,4096] (warm L2: same input every step)", lambda i: tpb.sum(xs[0], -1, out=ov), inb + 16384, 4096, 1, xs))

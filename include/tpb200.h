@@ -144,6 +144,32 @@ size_t tpb200_topk_workspace_bytes(int dtype, int ndim, const int64_t* sizes, co
 int tpb200_topk_plan_info(int dtype, int ndim, const int64_t* sizes, const int64_t* strides, int dim,
                           int64_t k, int64_t* info, int n_info);
 
+/* ---- softmax / log_softmax along one dim --------------------------------------------------------
+ * Replaces softmax_kernel_cudnn / log_softmax_kernel_cudnn (p10/src/backend/cuda/ActivationKernels.cu:
+ * 136-181: cudnnSoftmaxForward on a 4-D padded descriptor with int dims); schema
+ *   softmax(Tensor self, int64_t dim, DType dtype=Undefined) -> Tensor      (native_functions.yaml:587-597)
+ * Arithmetic as the reference's CPU kernels (p10/src/backend/cpu/PointwiseKernels.cpp:519-546):
+ * m = max over dim (NaN never the maximum), e = exp(x - m), s = sum e; softmax = e / s,
+ * log_softmax = (x - m) - log s; no special cases, so NaN, +inf and all -inf rows give NaN where that
+ * chain of float operations does.  `out` is contiguous, same shape as the input.
+ * dim = last with unit stride: any strided view whose other dims collapse to at most two; any other
+ * dim: the tensor must be contiguous.  Other layouts return TPB200_ERR_UNSUPPORTED.  No workspace.
+ */
+int tpb200_softmax(int log, const void* in, int dtype, int ndim, const int64_t* sizes,
+                   const int64_t* strides, int dim, void* out, void* stream);
+
+/* ---- median of the whole tensor ---------------------------------------------------------------
+ * The reference has a CPU kernel only (p10/src/backend/cpu/ReductionKernels.cpp:874-901; schema
+ * median(Tensor self) -> Tensor, native_functions.yaml:796-799): element (n - 1) / 2 of the sorted
+ * values, i.e. the lower middle one for even n; NaN for an empty tensor.  Here NaNs rank after all
+ * numbers (the reference's std::nth_element leaves their place undefined); -0.0 and +0.0 are one
+ * value and +0.0 is returned for it.  `out` receives one float32.  Any strided view; the workspace
+ * (tpb200_median_workspace_bytes(), 8-byte aligned) needs no initialisation.
+ */
+int tpb200_median(const void* in, int dtype, int ndim, const int64_t* sizes, const int64_t* strides,
+                  void* out, void* workspace, size_t workspace_bytes, void* stream);
+size_t tpb200_median_workspace_bytes(void);
+
 /* ---- sharded whole-tensor reductions: per-GPU partial, then a rank-ordered combine ------------
  * No reference counterpart (the reference is single-GPU: p10/src/backend/cuda/CUDAAllocator.cpp:87-88).
  *

@@ -73,6 +73,10 @@ def lib() -> ctypes.CDLL:
             f.restype = ctypes.c_int
             f.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                           ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+        L.tpo_softmax.restype = ctypes.c_int
+        L.tpo_softmax.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
+        L.tpo_median.restype = ctypes.c_int
+        L.tpo_median.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
         _lib = L
     return _lib
 
@@ -93,6 +97,11 @@ def ref() -> ctypes.CDLL:
         L.tpref_reduce_more.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, _I64P, _I64P, ctypes.c_int,
                                         _I64P, ctypes.c_int, ctypes.c_double, ctypes.c_void_p, ctypes.c_int64]
         L.tpref_last_error.restype = ctypes.c_char_p
+        L.tpref_softmax.restype = ctypes.c_int
+        L.tpref_softmax.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, _I64P, _I64P, ctypes.c_int64,
+                                    ctypes.c_void_p, ctypes.c_int64]
+        L.tpref_median.restype = ctypes.c_int
+        L.tpref_median.argtypes = [ctypes.c_void_p, ctypes.c_int, _I64P, _I64P, ctypes.c_void_p]
         _ref = L
     return _ref
 
@@ -244,3 +253,56 @@ def truth64(op: str, x: np.ndarray, dims=None, keepdim: bool = False, correction
             v = ssq / max(0, n - correction)
         return np.sqrt(v) if op == "std" else v
     raise ValueError(op)
+
+
+def softmax(x: np.ndarray, dim: int, log: bool = False) -> np.ndarray:
+    """C restatement of softmax / log_softmax along `dim` (float32 chain of the reference)."""
+    assert x.dtype == np.float32 and x.ndim >= 1
+    d = dim % x.ndim
+    xc = np.ascontiguousarray(x)
+    outer = int(np.prod(x.shape[:d], dtype=np.int64))
+    inner = int(np.prod(x.shape[d + 1:], dtype=np.int64))
+    out = np.empty_like(xc)
+    rc = lib().tpo_softmax(int(log), xc.ctypes.data, outer, x.shape[d], inner, out.ctypes.data)
+    if rc != 0:
+        raise RuntimeError(f"tpo_softmax failed: {rc}")
+    return out
+
+
+def ref_softmax(x: np.ndarray, dim: int, log: bool = False) -> np.ndarray:
+    """The reference's own compiled CPU softmax / log_softmax."""
+    sizes, strides = _prep(x)
+    out = np.empty(x.shape, dtype=np.float32)
+    L = ref()
+    rc = L.tpref_softmax(int(log), x.ctypes.data, x.ndim, _arr(sizes), _arr(strides), int(dim), out.ctypes.data, out.size)
+    if rc != 0:
+        raise RuntimeError(L.tpref_last_error().decode())
+    return out
+
+
+def median(x: np.ndarray) -> np.float32:
+    """C restatement of the whole-tensor median (NaNs rank last)."""
+    xc = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    out = np.empty(1, dtype=np.float32)
+    rc = lib().tpo_median(xc.ctypes.data, xc.size, out.ctypes.data)
+    if rc != 0:
+        raise RuntimeError(f"tpo_median failed: {rc}")
+    return out[0]
+
+
+def ref_median(x: np.ndarray) -> np.float32:
+    sizes, strides = _prep(x)
+    out = np.empty(1, dtype=np.float32)
+    L = ref()
+    rc = L.tpref_median(x.ctypes.data, x.ndim, _arr(sizes), _arr(strides), out.ctypes.data)
+    if rc != 0:
+        raise RuntimeError(L.tpref_last_error().decode())
+    return out[0]
+
+
+def truth64_softmax(x: np.ndarray, dim: int, log: bool = False) -> np.ndarray:
+    x64 = x.astype(np.float64)
+    m = x64.max(axis=dim, keepdims=True)
+    e = np.exp(x64 - m)
+    s = e.sum(axis=dim, keepdims=True)
+    return (x64 - m) - np.log(s) if log else e / s

@@ -6,7 +6,7 @@
 // (p10/src/*.cpp, p10/src/backend/cpu/*Kernels.cpp and the file its generator emits); it
 // contains no reduction arithmetic of its own.  Every call goes through the reference's
 // generated Tensor methods and therefore through its Dispatcher:
-//   Tensor::sum/mean/max/min/argmax/argmin/var/std/prod/norm/all/any
+//   Tensor::sum/mean/max/min/argmax/argmin/var/std/prod/norm/all/any/softmax/log_softmax/median
 //   ->  DispatchStub::call(name, CPU, ...)
 //   ->  tensorplay::cpu::*_kernel   (p10/src/backend/cpu/ReductionKernels.cpp:72-872)
 #include "Tensor.h"
@@ -125,6 +125,38 @@ int tpref_reduce_more(int op, const float* in, int ndim, const int64_t* sizes, c
             if (rc.dtype() != DType::Float32) { g_err = "expected Float32 result"; return 4; }
             std::memcpy(out, rc.data_ptr<float>(), sizeof(float) * out_numel);
         }
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return 1;
+    }
+}
+
+// softmax (log = 0) / log_softmax (log = 1) along `dim` through Tensor::softmax / Tensor::log_softmax
+// (p10/src/backend/cpu/PointwiseKernels.cpp:519-546); out receives the result in row-major order.
+int tpref_softmax(int log, const float* in, int ndim, const int64_t* sizes, const int64_t* strides,
+                  int64_t dim, float* out, int64_t out_numel) {
+    try {
+        Tensor x = wrap(in, ndim, sizes, strides);
+        Tensor r = log ? x.log_softmax(dim, DType::Undefined) : x.softmax(dim, DType::Undefined);
+        if (r.numel() != out_numel) { g_err = "output element count mismatch"; return 3; }
+        Tensor rc = r.is_contiguous() ? r : r.clone();
+        if (rc.dtype() != DType::Float32) { g_err = "expected Float32 result"; return 4; }
+        std::memcpy(out, rc.data_ptr<float>(), sizeof(float) * out_numel);
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return 1;
+    }
+}
+
+// median of the whole tensor through Tensor::median (p10/src/backend/cpu/ReductionKernels.cpp:874-901).
+int tpref_median(const float* in, int ndim, const int64_t* sizes, const int64_t* strides, float* out) {
+    try {
+        Tensor x = wrap(in, ndim, sizes, strides);
+        Tensor r = x.median();
+        if (r.numel() != 1 || r.dtype() != DType::Float32) { g_err = "expected one Float32 value"; return 4; }
+        *out = *r.data_ptr<float>();
         return 0;
     } catch (const std::exception& e) {
         g_err = e.what();

@@ -404,3 +404,62 @@ int tpo_topk(const float* in, int64_t rows, int64_t len, int64_t row_stride, int
     free(h);
     return 0;
 }
+
+
+/* ---------------------------------------------------------------- softmax / log_softmax -------
+ * p10/src/backend/cpu/PointwiseKernels.cpp:519-546, step by step in float32:
+ *   max_val = input.max({dim}, true)     strict-compare scan from -inf (NaN never wins)
+ *   shifted = input - max_val
+ *   exp_val = shifted.exp()              expf
+ *   sum_exp = exp_val.sum({dim}, true)   sequential float32 accumulation along the dim
+ *   softmax = exp_val / sum_exp          log_softmax = shifted - log(sum_exp)
+ * in is contiguous [outer, C, inner]; out has the same layout. */
+int tpo_softmax(int log, const float* in, int64_t outer, int64_t C, int64_t inner, float* out) {
+    if (outer < 0 || C < 0 || inner < 0) return -1;
+    for (int64_t o = 0; o < outer; ++o) {
+        for (int64_t i = 0; i < inner; ++i) {
+            const float* p = in + o * C * inner + i;
+            float* q = out + o * C * inner + i;
+            float m = -INFINITY;
+            for (int64_t j = 0; j < C; ++j) {
+                const float x = p[j * inner];
+                if (x > m) m = x;
+            }
+            float s = 0.0f;
+            for (int64_t j = 0; j < C; ++j) {
+                const float e = expf(p[j * inner] - m);
+                q[j * inner] = e;
+                s += e;
+            }
+            if (log) {
+                const float ls = logf(s);
+                for (int64_t j = 0; j < C; ++j) q[j * inner] = (p[j * inner] - m) - ls;
+            } else {
+                for (int64_t j = 0; j < C; ++j) q[j * inner] = q[j * inner] / s;
+            }
+        }
+    }
+    return 0;
+}
+
+/* ---------------------------------------------------------------- median ----------------------
+ * p10/src/backend/cpu/ReductionKernels.cpp:874-901: element (n - 1) / 2 of the sorted values (the
+ * lower middle one for even n), NaN for an empty tensor.  The reference's std::nth_element leaves
+ * the place of NaNs undefined; here they rank after every number. */
+static int cmp_float_nan_last(const void* a, const void* b) {
+    const float x = *(const float*)a, y = *(const float*)b;
+    const int xn = x != x, yn = y != y;
+    if (xn || yn) return xn - yn;
+    return (x > y) - (x < y);
+}
+int tpo_median(const float* in, int64_t n, float* out) {
+    if (n < 0) return -1;
+    if (n == 0) { *out = NAN; return 0; }
+    float* t = (float*)malloc(sizeof(float) * (size_t)n);
+    if (!t) return -9;
+    memcpy(t, in, sizeof(float) * (size_t)n);
+    qsort(t, (size_t)n, sizeof(float), cmp_float_nan_last);
+    *out = t[(n - 1) / 2];
+    free(t);
+    return 0;
+}

@@ -27,6 +27,7 @@ SYMBOLS = [
     "tpb200_reduce_partial_workspace_bytes", "tpb200_reduce_combine", "tpb200_topk_merge",
     "tpb200_device_status", "tpb200_reduce_all_noalloc", "tpb200_exchange_buffer_bytes",
     "tpb200_reduce_fused_exchange", "tpb200_topk_plan_info", "tpb200_set_exchange_wait_polls",
+    "tpb200_softmax", "tpb200_median", "tpb200_median_workspace_bytes",
 ]
 
 _I64P = ctypes.POINTER(ctypes.c_int64)
@@ -77,6 +78,12 @@ def lib() -> ctypes.CDLL:
     L.tpb200_exchange_buffer_bytes.argtypes = []
     L.tpb200_reduce_fused_exchange.restype = i
     L.tpb200_reduce_fused_exchange.argtypes = [i, vp, i, i64, i64, i64, i64, i, i, ctypes.POINTER(ctypes.c_void_p), vp, vp, vp, sz, vp]
+    L.tpb200_softmax.restype = i
+    L.tpb200_softmax.argtypes = [i, vp, i, i, _I64P, _I64P, i, vp, vp]
+    L.tpb200_median.restype = i
+    L.tpb200_median.argtypes = [vp, i, i, _I64P, _I64P, vp, vp, sz, vp]
+    L.tpb200_median_workspace_bytes.restype = sz
+    L.tpb200_median_workspace_bytes.argtypes = []
     L.tpb200_set_exchange_wait_polls.restype = i
     L.tpb200_set_exchange_wait_polls.argtypes = [i]
     L.tpb200_topk_plan_info.restype = i

@@ -36,6 +36,7 @@ struct Previous {
     void* prod = nullptr; void* prod_dim = nullptr; void* norm = nullptr; void* norm_dim = nullptr;
     void* all = nullptr; void* all_dim = nullptr; void* any = nullptr; void* any_dim = nullptr;
     void* topk = nullptr;
+    void* softmax = nullptr; void* log_softmax = nullptr; void* median = nullptr;
 } g_prev;
 
 void* lookup(const char* name) {
@@ -265,6 +266,46 @@ std::tuple<Tensor, Tensor> tpb_topk(const Tensor& self, int64_t k, int64_t dim, 
             Tensor(indices.impl()->storage(), shape, vstrides, DType::Int64, 0)};
 }
 
+// softmax / log_softmax (native_functions.yaml:587-597; the reference's CUDA kernels are
+// softmax_kernel_cudnn / log_softmax_kernel_cudnn, ActivationKernels.cu:172-181).  Layouts the
+// kernels do not take (a non-contiguous tensor with dim != last) go to the kernel registered before.
+Tensor softmax_common(int log, void* prev, const char* name, const Tensor& self, int64_t dim, DType dtype) {
+    using Fn = Tensor (*)(const Tensor&, int64_t, DType);
+    if (!ours(self) || !same_dtype(dtype) || self.dim() == 0) return fallthrough<Fn>(prev, name, self, dim, dtype);
+    const int nd = (int)self.dim();
+    int64_t d = dim < 0 ? dim + nd : dim;
+    if (d < 0 || d >= nd) TP_THROW(RuntimeError, "Dimension out of range");
+    const IntList sizes = static_cast<IntList>(self.shape());
+    const IntList strides = self.strides();
+    Tensor out(sizes, DType::Float32, self.device());
+    const int rc = tpb200_softmax(log, self.data_ptr(), TPB200_F32, nd, sizes.data(), strides.data(), (int)d,
+                                  out.data_ptr(), nullptr);
+    if (rc == TPB200_ERR_UNSUPPORTED && prev) return reinterpret_cast<Fn>(prev)(self, dim, dtype);
+    if (rc != TPB200_OK) raise_last();
+    return out;
+}
+Tensor tpb_softmax(const Tensor& self, int64_t dim, DType dtype) {
+    return softmax_common(0, g_prev.softmax, "softmax", self, dim, dtype);
+}
+Tensor tpb_log_softmax(const Tensor& self, int64_t dim, DType dtype) {
+    return softmax_common(1, g_prev.log_softmax, "log_softmax", self, dim, dtype);
+}
+// median(Tensor self) -> Tensor (native_functions.yaml:796-799): the reference registers a CPU kernel
+// only; this gives CUDA tensors one.  Result: a 0-dim Float32 tensor on the input's device.
+Tensor tpb_median(const Tensor& self) {
+    if (!ours(self)) return fallthrough<Tensor (*)(const Tensor&)>(g_prev.median, "median", self);
+    const int nd = (int)self.dim();
+    const IntList sizes = static_cast<IntList>(self.shape());
+    const IntList strides = self.strides();
+    Tensor out(IntList{}, DType::Float32, self.device());
+    const size_t ws_bytes = tpb200_median_workspace_bytes();
+    Tensor ws(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    const int rc = tpb200_median(self.numel() ? self.data_ptr() : nullptr, TPB200_F32, nd, sizes.data(), strides.data(),
+                                 out.data_ptr(), ws.data_ptr(), ws_bytes, nullptr);
+    if (rc != TPB200_OK) raise_last();
+    return out;
+}
+
 }  // namespace
 
 namespace tensorplay {
@@ -282,6 +323,7 @@ TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
     g_prev.all = lookup("all");         g_prev.all_dim = lookup("all.dim");
     g_prev.any = lookup("any");         g_prev.any_dim = lookup("any.dim");
     g_prev.topk = lookup("topk");
+    g_prev.softmax = lookup("softmax"); g_prev.log_softmax = lookup("log_softmax"); g_prev.median = lookup("median");
     m.impl("sum", tpb_sum);             m.impl("sum.dim_IntList", tpb_sum_dim);
     m.impl("mean", tpb_mean);           m.impl("mean.dim", tpb_mean_dim);
     m.impl("max", tpb_max);             m.impl("max.dim", tpb_max_dim);
@@ -294,6 +336,8 @@ TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
     m.impl("all", tpb_all);             m.impl("all.dim", tpb_all_dim);
     m.impl("any", tpb_any);             m.impl("any.dim", tpb_any_dim);
     m.impl("topk", tpb_topk);
+    m.impl("softmax", tpb_softmax);     m.impl("log_softmax", tpb_log_softmax);
+    m.impl("median", tpb_median);
 }
 
 }  // namespace tensorplay

@@ -164,14 +164,31 @@ __device__ bool sel_final(unsigned long long* cand, int n, int k, int cap, unsig
     // those words are scattered bucket by bucket behind the candidates, and a word's rank inside its
     // bucket (a scan of some twenty words) then gives its final position: it is written straight to
     // the output.  No sort network at all.
-    auto bucket_of = [&](unsigned long long w) -> int {
-        int lo = 0, hi = 128;
+    // four words at a time: the seven steps of the four binary searches interleave, so that a thread
+    // has four shared-memory loads in flight instead of one
+    auto bucket_of4 = [&](const unsigned long long (&w)[4], int (&b)[4]) {
+        int lo[4] = {0, 0, 0, 0}, hi[4] = {128, 128, 128, 128};
 #pragma unroll
-        for (int step = 0; step < 7; ++step) { const int mid = (lo + hi) >> 1; if (sh.samp[mid] > w) lo = mid + 1; else hi = mid; }
-        return lo;
+        for (int step = 0; step < 7; ++step) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int mid = (lo[u] + hi[u]) >> 1;
+                if (sh.samp[mid] > w[u]) lo[u] = mid + 1; else hi[u] = mid;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) b[u] = lo[u];
     };
     if (!inplace) {
-        for (int i = tid; i < n; i += NT) atomicAdd(&sh.hist[bucket_of(cand[i])], 1);
+        for (int base = 0; base < n; base += 4 * NT) {
+            unsigned long long w[4];
+            int b[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { const int i = base + u * NT + tid; w[u] = i < n ? cand[i] : 0ull; }
+            bucket_of4(w, b);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (base + u * NT + tid < n) atomicAdd(&sh.hist[b[u]], 1);
+        }
         __syncthreads();
         if (tid < 32) {
             // exclusive prefix over the 129 buckets (five per lane) and the bucket in which the k-th word lies
@@ -197,23 +214,36 @@ __device__ bool sel_final(unsigned long long* cand, int n, int k, int cap, unsig
         TPB_STAMP(11);
         if (n + T <= cap) {
             unsigned long long* tmp = cand + n;
-            for (int i = tid; i < n; i += NT) {
-                const unsigned long long w = cand[i];
-                const int bb = bucket_of(w);
-                if (bb <= bstar) tmp[sh.start[bb] + atomicAdd(&sh.fill[bb], 1)] = w;
+            for (int base = 0; base < n; base += 4 * NT) {
+                unsigned long long w[4];
+                int b[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) { const int i = base + u * NT + tid; w[u] = i < n ? cand[i] : 0ull; }
+                bucket_of4(w, b);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (base + u * NT + tid < n && b[u] <= bstar) tmp[sh.start[b[u]] + atomicAdd(&sh.fill[b[u]], 1)] = w[u];
             }
             __syncthreads();
             TPB_STAMP(12);
             TPB_NOTE(14, T);
-            for (int p = tid; p < T; p += NT) {
-                const unsigned long long w = tmp[p];
-                const int bb = bucket_of(w);
-                const int s0 = sh.start[bb], s1 = s0 + sh.hist[bb];
-                int pos = s0;
-                for (int q = s0; q < s1; ++q) pos += tmp[q] > w ? 1 : 0;
-                if (pos < k) {
-                    if (pos == k - 1 && (unsigned)(w >> 32) < tstar) sh.tmp = 1;
-                    emit(pos, w);
+            for (int base = 0; base < T; base += 4 * NT) {
+                unsigned long long w[4];
+                int b[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) { const int p = base + u * NT + tid; w[u] = p < T ? tmp[p] : 0ull; }
+                bucket_of4(w, b);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (base + u * NT + tid >= T) continue;
+                    const int s0 = sh.start[b[u]], s1 = s0 + sh.hist[b[u]];
+                    int pos = s0;
+#pragma unroll 4
+                    for (int q = s0; q < s1; ++q) pos += tmp[q] > w[u] ? 1 : 0;
+                    if (pos < k) {
+                        if (pos == k - 1 && (unsigned)(w[u] >> 32) < tstar) sh.tmp = 1;
+                        emit(pos, w[u]);
+                    }
                 }
             }
             __syncthreads();

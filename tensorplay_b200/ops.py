@@ -12,6 +12,8 @@ Names, argument meaning and error behaviour follow the reference's Tensor method
     norm(x, p=2.0, dim=None, keepdim=False)             p in {1, 2, inf, -inf}
     all(x, dim=None, keepdim=False) / any(...)          -> bool tensor
     topk(x, k, dim=-1, largest=True, sorted=True) -> (values, indices)   [new operator]
+    softmax(x, dim, dtype=None) / log_softmax(x, dim, dtype=None)
+    median(x)                                            -> 0-dim tensor, whole tensor only
     max_with_indices / min_with_indices(x, dim, keepdim=False) -> (values, indices), one pass
 
 `dim` may be an int, a list of ints (sum/mean/var/std/max/min) or None.  Tensors are torch CUDA
@@ -253,3 +255,53 @@ def topk(x, k, dim=-1, largest=True, sorted=True, *, out=None):
         ov = ov_c.movedim(-1, d)
         oi = oi_c.movedim(-1, d)
     return ov, oi
+
+
+def _softmax(log: bool, x, dim, dtype, out, what):
+    _check_input(x, what)
+    _check_dtype(dtype, what)
+    nd = x.dim()
+    if not isinstance(dim, int):
+        raise TypeError(f"{what}(): dim must be an int")
+    d = dim + nd if dim < 0 else dim
+    if d < 0 or d >= nd:     # a 0-dim tensor has no valid dim
+        raise RuntimeError("Dimension out of range")
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        if out is not None:
+            _check_out(out, list(x.shape), torch.float32, x.device, what)
+        else:
+            out = torch.empty(list(x.shape), dtype=torch.float32, device=x.device)
+        rc = L.tpb200_softmax(int(log), x.data_ptr(), _lib.F32, nd, _lib.i64_array(list(x.shape)),
+                              _lib.i64_array(list(x.stride())), d, out.data_ptr(),
+                              torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc)
+    return out
+
+
+def softmax(x, dim, dtype=None, *, out=None):
+    """softmax (config/native_functions.yaml:587-591): exp(x - max) / sum along `dim`."""
+    return _softmax(False, x, dim, dtype, out, "softmax")
+
+
+def log_softmax(x, dim, dtype=None, *, out=None):
+    """log_softmax (config/native_functions.yaml:593-597): (x - max) - log(sum exp(x - max))."""
+    return _softmax(True, x, dim, dtype, out, "log_softmax")
+
+
+def median(x, *, out=None):
+    """median (config/native_functions.yaml:796-799): element (n - 1) / 2 of the sorted values of the
+    whole tensor -- the lower middle one for even n -- as a 0-dim tensor; NaN for an empty tensor."""
+    _check_input(x, "median")
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        if out is not None:
+            _check_out(out, [], torch.float32, x.device, "median")
+        else:
+            out = torch.empty([], dtype=torch.float32, device=x.device)
+        ws = _workspace(x.device, L.tpb200_median_workspace_bytes())
+        rc = L.tpb200_median(x.data_ptr() if x.numel() else None, _lib.F32, x.dim(), _lib.i64_array(list(x.shape)),
+                             _lib.i64_array(list(x.stride())), out.data_ptr(), ws.data_ptr(), ws.numel(),
+                             torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc)
+    return out

@@ -151,6 +151,12 @@ int main() {
         try { gt2.topk(C + 1, -1, true, true); printf("FAIL: no error for k > len\n"); ++fails; }
         catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "selected index k out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }
     }
+    // softmax / log_softmax (the reference's CUDA kernels for them are cuDNN calls) and median (CPU only
+    // in the reference) through the same Dispatcher
+    close_f("softmax(dim=1)", g.softmax(1, DType::Undefined), c.softmax(1, DType::Undefined), 1e-5, 1e-30);
+    close_f("softmax(dim=0)", g.softmax(0, DType::Undefined), c.softmax(0, DType::Undefined), 1e-5, 1e-30);
+    close_f("log_softmax(dim=-1)", g.log_softmax(-1, DType::Undefined), c.log_softmax(-1, DType::Undefined), 1e-5, 1e-6);
+    equal_bits("median()", g.median(), c.median());
     // errors keep the reference's type and message
     try { g.sum({2}, false, DType::Undefined); printf("FAIL: no error for a bad dim\n"); ++fails; }
     catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "Dimension out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }

@@ -1,4 +1,4 @@
-"""Generates tests/golden/reduce_golden.npz from the REFERENCE's own compiled CPU code
+"""Generates tests/golden/reduce_golden.npz and tests/golden/softmax_median_golden.npz from the REFERENCE's own compiled CPU code
 (oracle/_ref/libtpref.so, built by oracle/build_ref.sh from a TensorPlay checkout).
 
 Run where the checkout exists:   python tests/golden/make_golden.py
@@ -66,6 +66,34 @@ def main():
         n += 1
     arrays["index_json"] = np.frombuffer(json.dumps(index).encode(), dtype=np.uint8)
     out = os.path.join(HERE, "reduce_golden.npz")
+    np.savez_compressed(out, **arrays)
+    print(f"wrote {out}: {len(index)} results, {os.path.getsize(out)} bytes")
+    more()
+
+
+def more():
+    """softmax / log_softmax along every dim and the whole-tensor median, from the reference's
+    compiled CPU kernels (PointwiseKernels.cpp:519-546, ReductionKernels.cpp:874-901)."""
+    rng = np.random.default_rng(2025)
+    arrays, index = {}, []
+    xs = [rng.standard_normal((7,)).astype(np.float32), (rng.standard_normal((6, 130)) * 3).astype(np.float32),
+          rng.standard_normal((3, 9, 5)).astype(np.float32), rng.uniform(-30, 30, (4, 1500)).astype(np.float32)]
+    xs[1][2, 5] = xs[1][2, 9] = xs[1][2].max() + 1.0            # tied maxima
+    xs[2][1, :, 2] = -np.inf
+    xs[2][1, 3, 2] = 0.5                                        # -inf beside one number
+    for n, x in enumerate(xs):
+        arrays[f"x{n}"] = x
+        for d in range(x.ndim):
+            for log in (0, 1):
+                key = f"s{len(index)}"
+                arrays[key] = O.ref_softmax(x, d, bool(log))
+                index.append({"x": f"x{n}", "op": "log_softmax" if log else "softmax", "dim": d, "out": key})
+        key = f"s{len(index)}"
+        arrays[key] = np.array([O.ref_median(x[np.isfinite(x)].copy())], dtype=np.float32)   # numbers only: nth_element and NaN / inf ties
+        arrays[f"m{n}"] = x[np.isfinite(x)].copy()
+        index.append({"x": f"m{n}", "op": "median", "dim": None, "out": key})
+    arrays["index_json"] = np.frombuffer(json.dumps(index).encode(), dtype=np.uint8)
+    out = os.path.join(HERE, "softmax_median_golden.npz")
     np.savez_compressed(out, **arrays)
     print(f"wrote {out}: {len(index)} results, {os.path.getsize(out)} bytes")
 

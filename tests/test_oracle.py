@@ -144,3 +144,47 @@ def test_topk_forms_agree_and_follow_the_contract():
     assert np.array_equal(O.topk(y, 1, -1, False)[1][:, 0], O.reduce("argmin", y, [1]))
     with pytest.raises(RuntimeError):
         O.topk(y, 301)
+
+
+GOLDEN2 = os.path.join(os.path.dirname(__file__), "golden", "softmax_median_golden.npz")
+
+
+def test_softmax_and_median_against_golden_fixture():
+    """softmax / log_softmax / median of the restatement, bit-exact against results of the reference's
+    compiled CPU code (tests/golden/make_golden.py)."""
+    z = np.load(GOLDEN2)
+    index = json.loads(bytes(z["index_json"]).decode())
+    assert len(index) >= 20
+    for e in index:
+        x = z[e["x"]]
+        if e["op"] == "median":
+            assert same(np.array([O.median(x)], dtype=np.float32), z[e["out"]]), e
+        else:
+            assert same(O.softmax(x, e["dim"], e["op"] == "log_softmax"), z[e["out"]]), e
+
+
+def test_softmax_special_rows_and_median_rules():
+    x = np.array([[1.0, np.nan, 2.0], [-np.inf, -np.inf, -np.inf], [0.0, np.inf, 1.0], [-np.inf, 0.0, 0.0]], dtype=np.float32)
+    s = O.softmax(x, 1)
+    assert np.isnan(s[0]).all() and np.isnan(s[1]).all() and np.isnan(s[2]).all()      # the float chain gives NaN
+    assert s[3].tolist() == [0.0, 0.5, 0.5]
+    ls = O.softmax(x, 1, True)
+    assert ls[3][0] == -np.inf and abs(ls[3][1] + np.log(2.0)) < 1e-6
+    assert O.median(np.array([3.0, 1.0, 2.0, 4.0], dtype=np.float32)) == 2.0             # lower middle of an even count
+    assert O.median(np.array([5.0], dtype=np.float32)) == 5.0
+    assert np.isnan(O.median(np.empty(0, dtype=np.float32)))
+    assert O.median(np.array([np.nan, 1.0, 2.0], dtype=np.float32)) == 2.0               # NaNs rank last
+    assert np.isnan(O.median(np.array([np.nan, np.nan, 2.0], dtype=np.float32)))
+
+
+@pytest.mark.skipif(not O.have_ref(), reason="the reference's CPU path is not compiled here")
+def test_softmax_and_median_against_compiled_reference():
+    rng = np.random.default_rng(8)
+    for shape in ((9,), (4, 257), (3, 5, 7), (2, 3, 4, 5)):
+        x = (rng.standard_normal(shape) * 4).astype(np.float32)
+        for d in range(x.ndim):
+            for log in (False, True):
+                assert same(O.softmax(x, d, log), O.ref_softmax(x, d, log)), (shape, d, log)
+        assert O.median(x) == O.ref_median(x), shape
+    t = rng.integers(0, 4, 1000).astype(np.float32)       # ties around the middle
+    assert O.median(t) == O.ref_median(t)
