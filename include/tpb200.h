@@ -219,6 +219,38 @@ int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, int64_t n, i
                                  void* const* peer_buffers, void* out_val, int64_t* out_idx,
                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- single-process multi-GPU host -------------------------------------------------------------
+ * No reference counterpart (the reference is single-GPU: p10/src/backend/cuda/CUDAAllocator.cpp:87-88).
+ * For a host that drives several GPUs of one box from one process (a C++ TensorPlay program; no
+ * Python, no PyTorch, no NCCL needed): a comm owns a stream, the exchange buffer, scratch and gather
+ * buffers on each of its GPUs -- all allocated by tpb200_comm_create -- and the two calls below run a
+ * whole-tensor reduction or a global top-k over a flat tensor whose partition g (counts[g] contiguous
+ * float32 elements at parts[g]) lives on GPU g of the comm.  Partition g starts at element
+ * counts[0] + ... + counts[g-1] of the whole tensor; indices in the results are global.
+ *   - Distinct GPUs with peer access: reductions use tpb200_reduce_fused_exchange on every GPU (records
+ *     cross NVLink by peer stores inside the kernels).  Otherwise -- e.g. one device listed several times,
+ *     which is how the tests emulate ranks on a single GPU -- records and candidates are copied between
+ *     the gather buffers and merged in rank order; no kernel then waits for another.
+ *   - The calls enqueue on the comm's streams and return; out_val[g] / out_idx[g] (device pointers on
+ *     GPU g, or NULL to use the comm's own result buffers, tpb200_comm_result_values / _indices) hold the
+ *     result -- identical on every GPU -- after tpb200_comm_synchronize (or a wait on
+ *     tpb200_comm_stream(comm, g)).  Inputs must be ready when the call is made.
+ *   - tpb200_topk_sharded: every GPU must hold at least k elements; k <= 2048 and GPUs * k <= 8192.
+ */
+typedef struct tpb200_comm tpb200_comm;
+int tpb200_comm_create(int n_gpus, const int* devices, tpb200_comm** out);
+int tpb200_comm_destroy(tpb200_comm* comm);
+int tpb200_comm_size(const tpb200_comm* comm);
+int tpb200_comm_fused(const tpb200_comm* comm);          /* 1: reductions exchange by peer stores */
+void* tpb200_comm_stream(const tpb200_comm* comm, int g);  /* cudaStream_t of GPU g */
+int tpb200_comm_synchronize(tpb200_comm* comm);
+void* tpb200_comm_result_values(const tpb200_comm* comm, int g);
+int64_t* tpb200_comm_result_indices(const tpb200_comm* comm, int g);
+int tpb200_reduce_sharded(tpb200_comm* comm, int op, const void* const* parts, const int64_t* counts, int dtype,
+                          int64_t correction, void* const* out_val, int64_t* const* out_idx);
+int tpb200_topk_sharded(tpb200_comm* comm, const void* const* parts, const int64_t* counts, int dtype, int64_t k,
+                        int largest, float* const* out_val, int64_t* const* out_idx);
+
 /* ---- global top-k over candidate lists --------------------------------------------------------
  * Final step of a sharded top-k: `n_cand` candidates (value, int64 GLOBAL index), e.g. the
  * all-gathered local top-k lists of every GPU, are reduced to the best k under the same order

@@ -28,6 +28,9 @@ SYMBOLS = [
     "tpb200_device_status", "tpb200_reduce_all_noalloc", "tpb200_exchange_buffer_bytes",
     "tpb200_reduce_fused_exchange", "tpb200_topk_plan_info", "tpb200_set_exchange_wait_polls",
     "tpb200_softmax", "tpb200_median", "tpb200_median_workspace_bytes",
+    "tpb200_comm_create", "tpb200_comm_destroy", "tpb200_comm_size", "tpb200_comm_fused", "tpb200_comm_stream",
+    "tpb200_comm_synchronize", "tpb200_comm_result_values", "tpb200_comm_result_indices",
+    "tpb200_reduce_sharded", "tpb200_topk_sharded",
 ]
 
 _I64P = ctypes.POINTER(ctypes.c_int64)
@@ -84,6 +87,27 @@ def lib() -> ctypes.CDLL:
     L.tpb200_median.argtypes = [vp, i, i, _I64P, _I64P, vp, vp, sz, vp]
     L.tpb200_median_workspace_bytes.restype = sz
     L.tpb200_median_workspace_bytes.argtypes = []
+    vpp = ctypes.POINTER(vp)
+    L.tpb200_comm_create.restype = i
+    L.tpb200_comm_create.argtypes = [i, ctypes.POINTER(i), vpp]
+    L.tpb200_comm_destroy.restype = i
+    L.tpb200_comm_destroy.argtypes = [vp]
+    L.tpb200_comm_size.restype = i
+    L.tpb200_comm_size.argtypes = [vp]
+    L.tpb200_comm_fused.restype = i
+    L.tpb200_comm_fused.argtypes = [vp]
+    L.tpb200_comm_stream.restype = vp
+    L.tpb200_comm_stream.argtypes = [vp, i]
+    L.tpb200_comm_synchronize.restype = i
+    L.tpb200_comm_synchronize.argtypes = [vp]
+    L.tpb200_comm_result_values.restype = vp
+    L.tpb200_comm_result_values.argtypes = [vp, i]
+    L.tpb200_comm_result_indices.restype = vp
+    L.tpb200_comm_result_indices.argtypes = [vp, i]
+    L.tpb200_reduce_sharded.restype = i
+    L.tpb200_reduce_sharded.argtypes = [vp, i, vpp, _I64P, i, i64, vpp, vpp]
+    L.tpb200_topk_sharded.restype = i
+    L.tpb200_topk_sharded.argtypes = [vp, vpp, _I64P, i, i64, i, vpp, vpp]
     L.tpb200_set_exchange_wait_polls.restype = i
     L.tpb200_set_exchange_wait_polls.argtypes = [i]
     L.tpb200_topk_plan_info.restype = i

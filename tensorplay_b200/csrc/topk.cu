@@ -1117,6 +1117,10 @@ static bool plan_select(long long rows, long long len, long long k, int sms, Top
     int on = 1;
     if (env_int("TPB200_TOPK_SELECT", &on) && on == 0) return false;
     if (k < 1 || k > kMaxStreamK || len < 32 * 1024 || rows > 0x3fffffffLL / kSelMaxCluster) return false;
+    // k <= 64 with enough rows to fill the GPU on their own: the ring kernel (one CTA per row, no
+    // cluster, 9 KB of shared memory) is as fast or faster -- measured on [256,151936], k = 50: 30.5 us
+    // against 30.7 us (two CTAs per row) and 32.5-34.4 us (one); on [512, 2^20], k = 64: 304 against 310 us
+    if (k <= kSmallK && rows * 4 >= (long long)sms * 2 * 3 && !(env_int("TPB200_TOPK_SELECT", &on) && on == 2)) return false;
     const long long tiles = len / kWarpTile;
     const int cap = (int)std::min<long long>(8192, std::max<long long>(4096, round_up(6 * k, 256)));
     const size_t smem = (size_t)cap * 8 + 4096;     // per CTA, with the static part

@@ -530,6 +530,28 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
             n += rem;
         }
         __syncthreads();
+        if (!bad) {
+            // Every CTA took what reached ITS key; only words that reach the largest key T* can be in the
+            // output if the check below holds (at least k of them), so the others are dropped here: the
+            // cut works on fewer words.  In place: a word only moves to a lower position, and a batch is
+            // read completely before any of it is written.
+            const unsigned long long floor_word = (unsigned long long)tstar << 32;
+            if (tid == 0) sh.tmp = 0;
+            for (int base = 0; base < n; base += NT) {
+                const int i = base + tid;
+                const unsigned long long w = i < n ? cand[i] : 0ull;
+                const bool keep = i < n && w >= floor_word;
+                const unsigned bal = __ballot_sync(kFull, keep);
+                int wb = 0;
+                __syncthreads();
+                if (lane == 0 && bal) wb = atomicAdd(&sh.tmp, __popc(bal));
+                wb = __shfl_sync(kFull, wb, 0);
+                if (keep) cand[wb + __popc(bal & ((1u << lane) - 1u))] = w;
+            }
+            __syncthreads();
+            n = sh.tmp;
+            __syncthreads();
+        }
         TPB_STAMP(4);
     }
 

@@ -155,7 +155,7 @@ int main() {
     // in the reference) through the same Dispatcher
     close_f("softmax(dim=1)", g.softmax(1, DType::Undefined), c.softmax(1, DType::Undefined), 1e-5, 1e-30);
     close_f("softmax(dim=0)", g.softmax(0, DType::Undefined), c.softmax(0, DType::Undefined), 1e-5, 1e-30);
-    close_f("log_softmax(dim=-1)", g.log_softmax(-1, DType::Undefined), c.log_softmax(-1, DType::Undefined), 1e-5, 1e-6);
+    close_f("log_softmax(dim=-1)", g.log_softmax(-1, DType::Undefined), c.log_softmax(-1, DType::Undefined), 1e-5, 1e-5);
     equal_bits("median()", g.median(), c.median());
     // errors keep the reference's type and message
     try { g.sum({2}, false, DType::Undefined); printf("FAIL: no error for a bad dim\n"); ++fails; }

@@ -107,3 +107,17 @@ def test_topk_slices_fit_the_merge_kernel(lib, monkeypatch):
     # rows ride on grid.x: more than 65535 long rows plan without an error
     assert lib.tpb200_topk(None, 0, 2, i64([70000, 8192]), i64([8192, 1]), 1, 5, 1, 1, None, None, None, 0, None) == _lib.ERR_INVALID
     assert b"input pointer is NULL" in lib.tpb200_last_error()
+
+
+def test_comm_argument_checks_need_no_gpu(lib):
+    """The single-process multi-GPU host refuses bad arguments before it touches a device."""
+    from tensorplay_b200 import _lib
+    comm = ctypes.c_void_p()
+    devs = (ctypes.c_int * 1)(0)
+    assert lib.tpb200_comm_create(0, devs, ctypes.byref(comm)) == _lib.ERR_UNSUPPORTED
+    assert lib.tpb200_comm_create(17, devs, ctypes.byref(comm)) == _lib.ERR_UNSUPPORTED
+    assert lib.tpb200_comm_create(1, None, ctypes.byref(comm)) == _lib.ERR_INVALID
+    assert lib.tpb200_comm_create(1, devs, None) == _lib.ERR_INVALID
+    assert lib.tpb200_comm_size(None) == 0 and lib.tpb200_comm_destroy(None) == _lib.OK
+    assert lib.tpb200_reduce_sharded(None, 0, None, None, 0, 1, None, None) == _lib.ERR_INVALID
+    assert lib.tpb200_topk_sharded(None, None, None, 0, 4, 1, None, None) == _lib.ERR_INVALID

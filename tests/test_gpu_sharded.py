@@ -125,6 +125,78 @@ def test_fused_exchange_one_rank(cuda):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("G", [1, 2, 4, 8])
+def test_single_process_comm(cuda, G):
+    """tpb200_comm_*: the torch-free multi-GPU host of the C ABI.  With one physical GPU the G ranks
+    are the same device listed G times (records and candidates are then copied between the gather
+    buffers; no kernel waits for another); with G real GPUs the reductions exchange by peer stores."""
+    import ctypes
+    import torch
+    import tensorplay_b200 as tpb
+    from tensorplay_b200 import _lib
+    from oracle import oracle as O
+    L = _lib.lib()
+    ndev = torch.cuda.device_count()
+    devices = list(range(G)) if ndev >= G else [0] * G
+    comm = ctypes.c_void_p()
+    _lib.check(L.tpb200_comm_create(G, (ctypes.c_int * G)(*devices), ctypes.byref(comm)))
+    try:
+        assert L.tpb200_comm_size(comm) == G
+        assert L.tpb200_comm_fused(comm) == (1 if (G == 1 or ndev >= G) else 0)
+        n = (1 << 22) + 13 * G + 5
+        x = config4(n=n)
+        x[n - 77] = 3e4                      # the maximum in the last partition ...
+        x[n // 3] = 3e4                      # ... tied by an earlier element: the lower index wins
+        bounds = [tpb.flat_partition(n, g, G) for g in range(G)]
+        parts = [torch.from_numpy(x[a:b].copy()).to(torch.device("cuda", devices[g])) for g, (a, b) in enumerate(bounds)]
+        torch.cuda.synchronize()
+        pp = (ctypes.c_void_p * G)(*[p.data_ptr() for p in parts])
+        cc = (ctypes.c_int64 * G)(*[b - a for a, b in bounds])
+
+        for rep in range(2):
+            for op in ("sum", "mean", "var", "std", "max_argmax", "argmin"):
+                want_val = op != "argmin"
+                want_idx = op in ("max_argmax", "argmin")
+                ovs = [torch.full((1,), float("nan"), device=torch.device("cuda", devices[g])) for g in range(G)]
+                ois = [torch.full((1,), -5, dtype=torch.int64, device=torch.device("cuda", devices[g])) for g in range(G)]
+                torch.cuda.synchronize()
+                pv = (ctypes.c_void_p * G)(*[t.data_ptr() for t in ovs]) if want_val else None
+                pi = (ctypes.c_void_p * G)(*[t.data_ptr() for t in ois]) if want_idx else None
+                _lib.check(L.tpb200_reduce_sharded(comm, _lib.OP[op], pp, cc, 0, 1, pv, pi))
+                _lib.check(L.tpb200_comm_synchronize(comm))
+                for g in range(G):
+                    if op in ("sum", "mean", "var", "std"):
+                        assert_close64(ovs[g].cpu().numpy()[0], O.truth64(op, x), f"comm G={G} {op} gpu {g}")
+                        assert ovs[g].cpu().view(torch.int32).item() == ovs[0].cpu().view(torch.int32).item()
+                    if op == "max_argmax":
+                        assert ovs[g].item() == 3e4 and ois[g].item() == n // 3
+                    if op == "argmin":
+                        assert ois[g].item() == int(np.argmin(x))
+        # global top-k, tie-heavy: global index order decides
+        y = np.random.default_rng(61).integers(0, 300, n).astype(np.float32)
+        yparts = [torch.from_numpy(y[a:b].copy()).to(torch.device("cuda", devices[g])) for g, (a, b) in enumerate(bounds)]
+        torch.cuda.synchronize()
+        yp = (ctypes.c_void_p * G)(*[p.data_ptr() for p in yparts])
+        for k, largest in ((64, True), (1000, False)):
+            if G * k > 8192:
+                continue
+            tvs = [torch.empty(k, device=torch.device("cuda", devices[g])) for g in range(G)]
+            tis = [torch.empty(k, dtype=torch.int64, device=torch.device("cuda", devices[g])) for g in range(G)]
+            torch.cuda.synchronize()
+            pv = (ctypes.c_void_p * G)(*[t.data_ptr() for t in tvs])
+            pi = (ctypes.c_void_p * G)(*[t.data_ptr() for t in tis])
+            _lib.check(L.tpb200_topk_sharded(comm, yp, cc, 0, k, int(largest), pv, pi))
+            _lib.check(L.tpb200_comm_synchronize(comm))
+            wv, wi = O.topk(y[None, :], k, -1, largest)
+            for g in range(G):
+                assert np.array_equal(tis[g].cpu().numpy(), wi[0]), (G, k, g)
+                assert np.array_equal(tvs[g].cpu().numpy().view(np.uint32), wv[0].view(np.uint32))
+        assert L.tpb200_topk_sharded(comm, yp, cc, 0, 5000, 1, None, None) == _lib.ERR_UNSUPPORTED
+    finally:
+        _lib.check(L.tpb200_comm_destroy(comm))
+    assert _lib.device_status() == 0
+
+
 def test_fused_exchange_wait_runs_out(cuda):
     """A rank whose peer never arrives: the wait is bounded, the kernel returns by itself with status 5
     and poisoned outputs (NaN / -1, not the previous call's answer), and the next call works.  Rank 1

@@ -4,8 +4,9 @@ softmax and log_softmax are float32 chains with exp and log in them: the result 
     |gpu - float64| <= 1e-5 * |float64| + ABS
 of a float64 evaluation (ABS = 1e-37 for softmax, whose outputs may be denormal-small; 1e-6 for
 log_softmax, whose outputs cross zero at the row maximum), must agree with the reference's own float32
-chain (the oracle, pinned bit-for-bit to the compiled reference) to the same bound, and must put NaN
-exactly where that chain does.  The median is one element of the input: bit-exact.
+chain (the oracle, pinned bit-for-bit to the compiled reference) to that bound plus the chain's own
+distance from float64, and must put NaN and infinities exactly where that chain does.  The median is
+one element of the input: bit-exact.
 """
 import json
 import os
@@ -18,7 +19,8 @@ GOLDEN2 = os.path.join(os.path.dirname(__file__), "golden", "softmax_median_gold
 REL = 1e-5
 
 
-def close(got, want, abs_tol, what):
+def close(got, want, abs_tol, what, slack=None):
+    """|got - want| <= REL * |want| + abs_tol (+ slack, elementwise), same NaNs, same infinities."""
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, what
@@ -28,6 +30,8 @@ def close(got, want, abs_tol, what):
     fin = np.isfinite(want)
     err = np.abs(got[fin] - want[fin])
     tol = REL * np.abs(want[fin]) + abs_tol
+    if slack is not None:
+        tol = tol + np.asarray(slack, dtype=np.float64)[fin]
     assert np.all(err <= tol), f"{what}: max excess {np.max(err - tol):.3e}"
 
 
@@ -42,8 +46,14 @@ def check_softmax(cuda, x, dim, what=""):
         abs_tol = 1e-6 if log else 1e-37
         name = f"{what} {'log_' if log else ''}softmax shape={x.shape} dim={dim}"
         with np.errstate(all="ignore"):
-            close(got, O.truth64_softmax(x, dim, log), abs_tol, name + " vs float64")
-        close(got, O.softmax(x, dim, log), abs_tol, name + " vs reference chain")
+            truth = O.truth64_softmax(x, dim, log)
+            close(got, truth, abs_tol, name + " vs float64")
+            # against the reference's float32 chain: the same NaNs and infinities, and no further from it
+            # than the bound above plus the chain's own distance from float64 (its sequential float32
+            # sum is the less accurate of the two)
+            ref = O.softmax(x, dim, log)
+            own = np.abs(ref.astype(np.float64) - truth)
+            close(got, ref, abs_tol, name + " vs reference chain", slack=np.where(np.isfinite(own), own, 0.0))
 
 
 def test_softmax_rows_of_every_length(cuda):
@@ -59,7 +69,7 @@ def test_softmax_rows_of_every_length(cuda):
     bg = torch.from_numpy(base).to(cuda)
     for vn, vg in ((base[:, 1:], bg[:, 1:]), (base[::2], bg[::2])):
         got = tpb.softmax(vg, 1).cpu().numpy()
-        close(got, O.softmax(np.ascontiguousarray(vn), 1), 1e-37, "strided view")
+        close(got, O.truth64_softmax(np.ascontiguousarray(vn), 1), 1e-37, "strided view")
 
 
 def test_softmax_other_dims(cuda):
@@ -114,6 +124,7 @@ def test_softmax_headline_shapes(cuda):
 def test_softmax_and_median_golden(cuda):
     import torch
     import tensorplay_b200 as tpb
+    from oracle import oracle as O
     z = np.load(GOLDEN2)
     index = json.loads(bytes(z["index_json"]).decode())
     for e in index:
@@ -125,7 +136,9 @@ def test_softmax_and_median_golden(cuda):
         else:
             log = e["op"] == "log_softmax"
             got = (tpb.log_softmax if log else tpb.softmax)(xg, e["dim"]).cpu().numpy()
-            close(got, z[e["out"]], 1e-6 if log else 1e-37, str(e))
+            with np.errstate(all="ignore"):
+                own = np.abs(z[e["out"]].astype(np.float64) - O.truth64_softmax(x, e["dim"], log))
+            close(got, z[e["out"]], 1e-6 if log else 1e-37, str(e), slack=np.where(np.isfinite(own), own, 0.0))
 
 
 def test_median(cuda):

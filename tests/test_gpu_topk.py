@@ -12,7 +12,9 @@ pytestmark = pytest.mark.gpu
 def topk_path(request, monkeypatch):
     """Every test runs twice: with the sampled-threshold kernel (the default for long rows; it redoes
     the rows that fail its check with the scanning kernel's body) and with the scanning kernels alone."""
-    monkeypatch.setenv("TPB200_TOPK_SELECT", "1" if request.param == "select" else "0")
+    # "2": the sampled-threshold kernel wherever it applies, also where the planner would prefer the ring
+    # kernel (k <= 64 with rows enough to fill the GPU)
+    monkeypatch.setenv("TPB200_TOPK_SELECT", "2" if request.param == "select" else "0")
     return request.param
 
 
