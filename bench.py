@@ -277,6 +277,9 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
                 ("norm p=2 dim=1", lambda i: tpb.norm(xs[0], 2.0, 1, out=ov1), a * 512 * 4, a * 512, 2),
                 ("prod dims=(0,2)", lambda i: tpb.prod(xs[0], [0, 2], out=ov2), 16384, 4096, 1)]:
             cases.append(Case(f"{op} [{a},4096,512]", fn, inb + outb, rows, launches, xs))
+        # the permute copy the reference makes before argmin over dim 1 (ReductionKernels.cu:67-75): read + write
+        perm = torch.empty(a, 512, 4096, device=dev)
+        cases.append(Case(f"permute(0,2,1) copy [{a},4096,512]", lambda i: tpb.copy_(perm, xs[0].permute(0, 2, 1)), 2 * inb, a * 512, 1, xs))
     elif workload == "c4":
         # strong scaling: the 2^31-element tensor is split in flat partitions, one per rank
         total = 1 << 31

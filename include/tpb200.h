@@ -170,6 +170,18 @@ int tpb200_median(const void* in, int dtype, int ndim, const int64_t* sizes, con
                   void* out, void* workspace, size_t workspace_bytes, void* stream);
 size_t tpb200_median_workspace_bytes(void);
 
+/* ---- strided copy ------------------------------------------------------------------------------
+ * dst[i0, i1, ...] = src[i0, i1, ...] for two views of the same shape (sizes) with their own strides,
+ * 4-byte elements (TPB200_F32; the bits are copied, so int32 data works as well).  Replaces
+ * copy_cast_kernel_impl (p10/src/backend/cuda/CopyKernels.cu:42-53, launched at :105-156: one element
+ * per thread, a div/mod chain over every dim on both sides) for what callers do around reductions:
+ * permute().contiguous(), transposes, slices (ReductionKernels.cu:67-75, 143).  Coalesced on both sides
+ * whenever each view has a unit stride somewhere (shared-memory tiles when those are different dims).
+ * The views must not overlap each other; dst must not overlap itself (no zero strides in dst).
+ */
+int tpb200_strided_copy(void* dst, const int64_t* dst_strides, const void* src, const int64_t* src_strides,
+                        int dtype, int ndim, const int64_t* sizes, void* stream);
+
 /* ---- sharded whole-tensor reductions: per-GPU partial, then a rank-ordered combine ------------
  * No reference counterpart (the reference is single-GPU: p10/src/backend/cuda/CUDAAllocator.cpp:87-88).
  *

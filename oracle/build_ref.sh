@@ -9,7 +9,9 @@
 #      call generated Tensor methods (Tensor::mean, operator-, ...), so TensorGenerated.{h,cpp}
 #      is needed; only PyYAML is required.  The schema gets one additive entry (top-k, which the
 #      reference does not declare: tensorplay_b200/csrc/adapter/topk_schema.yaml), so that the
-#      generated Tensor class has the topk method the adapter check calls;
+#      generated Tensor class has the topk method the adapter check calls, and the derivatives get
+#      additive formulas for the dim variants of sum / mean / var / std
+#      (tensorplay_b200/csrc/adapter/derivatives_add.yaml), which the autograd check uses;
 #   2. g++ with the reference's own flags (CMakeLists.txt:213,470: -O3 -march=native, OpenMP on,
 #      no USE_CUDA / USE_ONEDNN / USE_MKL) on the P10 core and CPU kernel files;
 #   3. a link with oracle/ref_driver.cpp.
@@ -20,11 +22,12 @@ HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 REF="${TP_REFERENCE_ROOT:-}"
 OUT="$HERE/_ref"
 SCHEMA_ADD="$HERE/../tensorplay_b200/csrc/adapter/topk_schema.yaml"
+DERIV_ADD="$HERE/../tensorplay_b200/csrc/adapter/derivatives_add.yaml"
 if [ -z "$REF" ] || [ ! -f "$REF/p10/src/backend/cpu/ReductionKernels.cpp" ]; then
     echo "build_ref: TP_REFERENCE_ROOT does not name a TensorPlay checkout; skipping" >&2
     exit 0
 fi
-if [ -f "$OUT/libtpref.so" ] && [ "$OUT/libtpref.so" -nt "$HERE/ref_driver.cpp" ] && [ "$OUT/libtpref.so" -nt "$SCHEMA_ADD" ] && [ "${1:-}" != "--force" ]; then
+if [ -f "$OUT/libtpref.so" ] && [ "$OUT/libtpref.so" -nt "$HERE/ref_driver.cpp" ] && [ "$OUT/libtpref.so" -nt "$SCHEMA_ADD" ] && [ "$OUT/libtpref.so" -nt "$DERIV_ADD" ] && [ "${1:-}" != "--force" ]; then
     echo "build_ref: $OUT/libtpref.so is up to date"
     exit 0
 fi
@@ -35,8 +38,12 @@ trap 'rm -rf "$PKG_SCRATCH"' EXIT
 cat "$REF/config/native_functions.yaml" > "$OUT/native_functions_plus_topk.yaml"
 printf '\n' >> "$OUT/native_functions_plus_topk.yaml"
 grep -v '^#' "$SCHEMA_ADD" >> "$OUT/native_functions_plus_topk.yaml"
+# ... and its derivatives plus the additive formulas for the dim variants of the reductions
+cat "$REF/config/derivatives.yaml" > "$OUT/derivatives_plus_dims.yaml"
+printf '\n' >> "$OUT/derivatives_plus_dims.yaml"
+grep -v '^#' "$DERIV_ADD" >> "$OUT/derivatives_plus_dims.yaml"
 python3 "$REF/tools/codegen/gen.py" --yaml "$OUT/native_functions_plus_topk.yaml" \
-    --derivatives "$REF/config/derivatives.yaml" --out_dir "$OUT/gen/tensorplay/ops" \
+    --derivatives "$OUT/derivatives_plus_dims.yaml" --out_dir "$OUT/gen/tensorplay/ops" \
     --pkg_out "$PKG_SCRATCH" > "$OUT/gen.log" 2>&1
 
 CXXFLAGS="-std=c++20 -O3 -march=native -fopenmp -w -fPIC -I$REF/p10/include -I$OUT/gen"

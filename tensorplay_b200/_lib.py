@@ -30,7 +30,7 @@ SYMBOLS = [
     "tpb200_softmax", "tpb200_median", "tpb200_median_workspace_bytes",
     "tpb200_comm_create", "tpb200_comm_destroy", "tpb200_comm_size", "tpb200_comm_fused", "tpb200_comm_stream",
     "tpb200_comm_synchronize", "tpb200_comm_result_values", "tpb200_comm_result_indices",
-    "tpb200_reduce_sharded", "tpb200_topk_sharded",
+    "tpb200_reduce_sharded", "tpb200_topk_sharded", "tpb200_strided_copy",
 ]
 
 _I64P = ctypes.POINTER(ctypes.c_int64)
@@ -108,6 +108,8 @@ def lib() -> ctypes.CDLL:
     L.tpb200_reduce_sharded.argtypes = [vp, i, vpp, _I64P, i, i64, vpp, vpp]
     L.tpb200_topk_sharded.restype = i
     L.tpb200_topk_sharded.argtypes = [vp, vpp, _I64P, i, i64, i, vpp, vpp]
+    L.tpb200_strided_copy.restype = i
+    L.tpb200_strided_copy.argtypes = [vp, _I64P, vp, _I64P, i, i, _I64P, vp]
     L.tpb200_set_exchange_wait_polls.restype = i
     L.tpb200_set_exchange_wait_polls.argtypes = [i]
     L.tpb200_topk_plan_info.restype = i

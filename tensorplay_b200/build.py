@@ -15,7 +15,7 @@ _CSRC = os.path.join(_PKG, "csrc")
 _ROOT = os.path.dirname(_PKG)
 LIB_PATH = os.path.join(_PKG, "libtpb200.so")
 
-SOURCES = ["api_common.cu", "reduce.cu", "topk.cu", "softmax.cu", "median.cu", "comm.cu"]
+SOURCES = ["api_common.cu", "reduce.cu", "topk.cu", "softmax.cu", "median.cu", "comm.cu", "copy.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

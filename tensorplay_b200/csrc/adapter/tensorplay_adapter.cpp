@@ -12,12 +12,18 @@
 #include "Exception.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
+#include <cstdlib>
 #include <limits>
+#include <map>
+#include <mutex>
 #include <optional>
 #include <string>
 #include <tuple>
 #include <vector>
+
+#include <cuda_runtime_api.h>
 
 #include "../../../include/tpb200.h"
 
@@ -37,6 +43,7 @@ struct Previous {
     void* all = nullptr; void* all_dim = nullptr; void* any = nullptr; void* any_dim = nullptr;
     void* topk = nullptr;
     void* softmax = nullptr; void* log_softmax = nullptr; void* median = nullptr;
+    void* copy_ = nullptr;
 } g_prev;
 
 void* lookup(const char* name) {
@@ -48,6 +55,88 @@ void* lookup(const char* name) {
 }
 
 [[noreturn]] void raise_last() { TP_THROW(RuntimeError, std::string(tpb200_last_error())); }
+
+// Calls that reached the sm_100a kernels through this adapter (a diagnostic: tests use it to show that
+// TensorPlay's generated methods and its autograd nodes land here).
+std::atomic<long long> g_calls{0};
+
+// ---- device memory for results and scratch --------------------------------------------------
+// The reference's CUDA allocator does one cudaMalloc per tensor and one cudaFree per release
+// (p10/src/backend/cuda/CUDAAllocator.cpp:70-89), each of which synchronises the device: through the
+// Dispatcher a [4096,4096] row sum then takes 20 us for a 12 us kernel.  Results and scratch of this
+// adapter therefore come from a small cache of device blocks, wrapped as ordinary TensorPlay storage
+// (Storage(DataPtr(ptr, deleter, device), nbytes), p10/include/Storage.h:19-25): a released block goes
+// back to a free list of its size class and the next call of that size takes it without touching the
+// driver.  Safe because everything TensorPlay launches runs on the legacy default stream, so a block
+// that is reused is reused in stream order.  TPB200_ADAPTER_POOL=0 switches the cache off (the
+// reference's allocator is then used); at most kPoolLimit bytes are kept per device.
+namespace pool {
+constexpr size_t kPoolLimit = 1ull << 30;
+struct State {
+    std::mutex mu;
+    std::map<std::pair<int, size_t>, std::vector<void*>> free_;
+    std::map<int, size_t> cached;
+};
+State& state() { static State* s = new State; return *s; }   // never destroyed: blocks may outlive static teardown
+bool enabled() {
+    static const bool on = [] { const char* v = std::getenv("TPB200_ADAPTER_POOL"); return !(v && v[0] == '0'); }();
+    return on;
+}
+size_t size_class(size_t n) {
+    if (n <= 512) return 512;
+    if (n <= (1u << 20)) { size_t c = 512; while (c < n) c <<= 1; return c; }
+    return (n + (2u << 20) - 1) / (2u << 20) * (2u << 20);
+}
+void release(void* p, int dev, size_t cls) {
+    State& s = state();
+    std::lock_guard<std::mutex> lk(s.mu);
+    if (s.cached[dev] + cls <= kPoolLimit) {
+        s.free_[{dev, cls}].push_back(p);
+        s.cached[dev] += cls;
+        return;
+    }
+    int cur = 0;
+    cudaGetDevice(&cur);
+    cudaSetDevice(dev);
+    cudaFree(p);
+    cudaSetDevice(cur);
+}
+tensorplay::DataPtr allocate(size_t nbytes, const tensorplay::Device& device) {
+    const int dev = device.index() < 0 ? 0 : (int)device.index();
+    const size_t cls = size_class(nbytes ? nbytes : 1);
+    void* p = nullptr;
+    {
+        State& s = state();
+        std::lock_guard<std::mutex> lk(s.mu);
+        auto it = s.free_.find({dev, cls});
+        if (it != s.free_.end() && !it->second.empty()) {
+            p = it->second.back();
+            it->second.pop_back();
+            s.cached[dev] -= cls;
+        }
+    }
+    if (!p) {
+        int cur = 0;
+        cudaGetDevice(&cur);
+        if (cur != dev) cudaSetDevice(dev);
+        const cudaError_t e = cudaMalloc(&p, cls);
+        if (cur != dev) cudaSetDevice(cur);
+        if (e != cudaSuccess || !p) TP_THROW(RuntimeError, "CUDA Error: out of memory in the adapter's device cache");
+    }
+    return tensorplay::DataPtr(p, [dev, cls](void* q) { if (q) release(q, dev, cls); }, device);
+}
+}  // namespace pool
+
+// A fresh tensor on `device`: from the cache above, or through the reference's allocator.
+Tensor fresh(const IntList& shape, DType dtype, const tensorplay::Device& device) {
+    if (!pool::enabled()) return Tensor(shape, dtype, device);
+    size_t numel = 1;
+    for (int64_t v : shape) numel *= (size_t)v;
+    const size_t item = dtype == DType::Int64 ? 8 : (dtype == DType::Float32 ? 4 : 1);   // the dtypes this adapter makes
+    const size_t nbytes = numel * item;
+    tensorplay::Storage st(pool::allocate(nbytes, device), nbytes);
+    return Tensor(st, shape, dtype);
+}
 
 // (mask, output shape) for a dim list; an empty list reduces every dim.  Errors as
 // compute_reduction_shape (p10/src/backend/cpu/ReductionKernels.cpp:48-58).
@@ -77,10 +166,11 @@ Tensor run(int op, const Tensor& self, uint64_t mask, int index_dim, int64_t cor
     const IntList strides = self.strides();
     const bool idx = op == TPB200_OP_ARGMAX || op == TPB200_OP_ARGMIN;
     const bool boolean = op == TPB200_OP_ALL || op == TPB200_OP_ANY;
-    Tensor out(out_shape, idx ? DType::Int64 : (boolean ? DType::Bool : DType::Float32), self.device());
+    Tensor out = fresh(out_shape, idx ? DType::Int64 : (boolean ? DType::Bool : DType::Float32), self.device());
     const size_t ws_bytes = tpb200_reduce_workspace_bytes(op, TPB200_F32, nd, sizes.data(), strides.data(), mask);
     Tensor ws;
-    if (ws_bytes) ws = Tensor(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    if (ws_bytes) ws = fresh(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    g_calls.fetch_add(1, std::memory_order_relaxed);
     const int rc = tpb200_reduce(op, self.data_ptr(), TPB200_F32, nd, sizes.data(), strides.data(), mask, index_dim,
                                  correction, idx ? nullptr : out.data_ptr(), idx ? out.data_ptr<int64_t>() : nullptr,
                                  ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, nullptr);
@@ -242,11 +332,12 @@ std::tuple<Tensor, Tensor> tpb_topk(const Tensor& self, int64_t k, int64_t dim, 
     IntList inner;                                   // [other dims in their order..., k]
     for (int i = 0; i < nd; ++i) if (i != d) inner.push_back(sizes[i]);
     inner.push_back(k);
-    Tensor values(inner, DType::Float32, self.device());
-    Tensor indices(inner, DType::Int64, self.device());
+    Tensor values = fresh(inner, DType::Float32, self.device());
+    Tensor indices = fresh(inner, DType::Int64, self.device());
     const size_t ws_bytes = tpb200_topk_workspace_bytes(TPB200_F32, nd, sizes.data(), strides.data(), (int)d, k);
     Tensor ws;
-    if (ws_bytes) ws = Tensor(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    if (ws_bytes) ws = fresh(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    g_calls.fetch_add(1, std::memory_order_relaxed);
     const int rc = tpb200_topk(self.data_ptr(), TPB200_F32, nd, sizes.data(), strides.data(), (int)d, k, largest ? 1 : 0,
                                sorted ? 1 : 0, values.data_ptr(), indices.data_ptr<int64_t>(),
                                ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, nullptr);
@@ -277,7 +368,8 @@ Tensor softmax_common(int log, void* prev, const char* name, const Tensor& self,
     if (d < 0 || d >= nd) TP_THROW(RuntimeError, "Dimension out of range");
     const IntList sizes = static_cast<IntList>(self.shape());
     const IntList strides = self.strides();
-    Tensor out(sizes, DType::Float32, self.device());
+    Tensor out = fresh(sizes, DType::Float32, self.device());
+    g_calls.fetch_add(1, std::memory_order_relaxed);
     const int rc = tpb200_softmax(log, self.data_ptr(), TPB200_F32, nd, sizes.data(), strides.data(), (int)d,
                                   out.data_ptr(), nullptr);
     if (rc == TPB200_ERR_UNSUPPORTED && prev) return reinterpret_cast<Fn>(prev)(self, dim, dtype);
@@ -297,16 +389,43 @@ Tensor tpb_median(const Tensor& self) {
     const int nd = (int)self.dim();
     const IntList sizes = static_cast<IntList>(self.shape());
     const IntList strides = self.strides();
-    Tensor out(IntList{}, DType::Float32, self.device());
+    Tensor out = fresh(IntList{}, DType::Float32, self.device());
     const size_t ws_bytes = tpb200_median_workspace_bytes();
-    Tensor ws(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    Tensor ws = fresh(IntList{(int64_t)ws_bytes}, DType::UInt8, self.device());
+    g_calls.fetch_add(1, std::memory_order_relaxed);
     const int rc = tpb200_median(self.numel() ? self.data_ptr() : nullptr, TPB200_F32, nd, sizes.data(), strides.data(),
                                  out.data_ptr(), ws.data_ptr(), ws_bytes, nullptr);
     if (rc != TPB200_OK) raise_last();
     return out;
 }
 
+// copy_(Tensor& self, const Tensor& src) (native_functions.yaml; the reference's CUDA kernel is copy_kernel,
+// p10/src/backend/cuda/CopyKernels.cu:56-160).  Taken here: both tensors on the same CUDA device, the same
+// 4-byte dtype, the same shape, and at least one of them not contiguous -- the strided copies that
+// permute().contiguous() and friends make.  Everything else (casts, host sources, plain contiguous
+// copies, which the reference does with one cudaMemcpy) goes to the kernel registered before.
+Tensor& tpb_copy_(Tensor& self, const Tensor& src) {
+    using Fn = Tensor& (*)(Tensor&, const Tensor&);
+    const bool four = self.dtype() == src.dtype() && (self.dtype() == DType::Float32 || self.dtype() == DType::Int32 || self.dtype() == DType::UInt32);
+    const bool ours_ = four && self.device().is_cuda() && src.device().is_cuda() && self.device() == src.device() &&
+                       static_cast<IntList>(self.shape()) == static_cast<IntList>(src.shape()) &&
+                       !(self.is_contiguous() && src.is_contiguous()) && self.dim() <= TPB200_MAX_DIMS;
+    if (!ours_) {
+        if (!g_prev.copy_) TP_THROW(NotImplementedError, "copy_ not implemented for these tensors on CUDA");
+        return reinterpret_cast<Fn>(g_prev.copy_)(self, src);
+    }
+    const IntList sizes = static_cast<IntList>(self.shape());
+    const IntList ds = self.strides(), ss = src.strides();
+    g_calls.fetch_add(1, std::memory_order_relaxed);
+    const int rc = tpb200_strided_copy(self.data_ptr(), ds.data(), src.data_ptr(), ss.data(), TPB200_F32, (int)self.dim(),
+                                       sizes.data(), nullptr);
+    if (rc != TPB200_OK) raise_last();
+    return self;
+}
+
 }  // namespace
+
+extern "C" long long tpb200_adapter_calls(void) { return g_calls.load(std::memory_order_relaxed); }
 
 namespace tensorplay {
 
@@ -324,6 +443,7 @@ TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
     g_prev.any = lookup("any");         g_prev.any_dim = lookup("any.dim");
     g_prev.topk = lookup("topk");
     g_prev.softmax = lookup("softmax"); g_prev.log_softmax = lookup("log_softmax"); g_prev.median = lookup("median");
+    g_prev.copy_ = lookup("copy_");
     m.impl("sum", tpb_sum);             m.impl("sum.dim_IntList", tpb_sum_dim);
     m.impl("mean", tpb_mean);           m.impl("mean.dim", tpb_mean_dim);
     m.impl("max", tpb_max);             m.impl("max.dim", tpb_max_dim);
@@ -338,6 +458,7 @@ TENSORPLAY_LIBRARY_IMPL(CUDA, B200Reductions) {
     m.impl("topk", tpb_topk);
     m.impl("softmax", tpb_softmax);     m.impl("log_softmax", tpb_log_softmax);
     m.impl("median", tpb_median);
+    m.impl("copy_", tpb_copy_);
 }
 
 }  // namespace tensorplay

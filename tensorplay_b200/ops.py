@@ -14,6 +14,7 @@ Names, argument meaning and error behaviour follow the reference's Tensor method
     topk(x, k, dim=-1, largest=True, sorted=True) -> (values, indices)   [new operator]
     softmax(x, dim, dtype=None) / log_softmax(x, dim, dtype=None)
     median(x)                                            -> 0-dim tensor, whole tensor only
+    copy_(dst, src)                                      strided float32 copy (Tensor.copy_ / contiguous())
     max_with_indices / min_with_indices(x, dim, keepdim=False) -> (values, indices), one pass
 
 `dim` may be an int, a list of ints (sum/mean/var/std/max/min) or None.  Tensors are torch CUDA
@@ -305,3 +306,27 @@ def median(x, *, out=None):
                              torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc)
     return out
+
+
+def copy_(dst, src):
+    """dst.copy_(src) for two float32 CUDA views of the same shape with any strides (the reference's
+    copy_ on CUDA: p10/src/backend/cuda/CopyKernels.cu:56-160); returns dst."""
+    _check_input(src, "copy_")
+    _check_input(dst, "copy_")
+    if tuple(dst.shape) != tuple(src.shape) or dst.device != src.device:
+        raise RuntimeError("Sizes do not match for copy")
+    L = _lib.lib()
+    with torch.cuda.device(src.device):
+        rc = L.tpb200_strided_copy(dst.data_ptr(), _lib.i64_array(list(dst.stride())), src.data_ptr(),
+                                   _lib.i64_array(list(src.stride())), _lib.F32, src.dim(), _lib.i64_array(list(src.shape)),
+                                   torch.cuda.current_stream(src.device).cuda_stream)
+    _lib.check(rc)
+    return dst
+
+
+def contiguous(x):
+    """A contiguous copy of a float32 CUDA view (what permute().contiguous() costs the reference a
+    div/mod per element for)."""
+    _check_input(x, "contiguous")
+    out = torch.empty(list(x.shape), dtype=torch.float32, device=x.device)
+    return copy_(out, x)

@@ -157,6 +157,19 @@ int main() {
     close_f("softmax(dim=0)", g.softmax(0, DType::Undefined), c.softmax(0, DType::Undefined), 1e-5, 1e-30);
     close_f("log_softmax(dim=-1)", g.log_softmax(-1, DType::Undefined), c.log_softmax(-1, DType::Undefined), 1e-5, 1e-5);
     equal_bits("median()", g.median(), c.median());
+    // copy_ of a strided view (what permute().contiguous() runs): the transposed view built above into a
+    // fresh contiguous tensor, through the Dispatcher to the tiled copy kernel
+    {
+        Tensor dstg(std::vector<int64_t>{C, R}, DType::Float32, Device(DeviceType::CUDA, 0));
+        dstg.copy_(gt);
+        auto h = to_host<float>(dstg);
+        ++checks;
+        bool ok = true;
+        for (int64_t i = 0; i < C && ok; ++i)
+            for (int64_t j = 0; j < R; ++j)
+                if (std::memcmp(&h[i * R + j], &v[j * C + i], 4) != 0) { ok = false; break; }
+        if (!ok) { printf("FAIL copy_ of a transposed view\n"); ++fails; }
+    }
     // errors keep the reference's type and message
     try { g.sum({2}, false, DType::Undefined); printf("FAIL: no error for a bad dim\n"); ++fails; }
     catch (const std::exception& e) { ++checks; if (!std::strstr(e.what(), "Dimension out of range")) { printf("FAIL: message %s\n", e.what()); ++fails; } }

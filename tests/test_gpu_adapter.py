@@ -27,3 +27,19 @@ def test_tensorplay_dispatches_to_the_new_kernels(cuda):
     if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "dispatcher_latency.txt"), "w") as f:
             f.write("\n".join(lat) + "\n")
+
+
+TPX_BIN = os.path.join(ROOT, "oracle", "_ref", "tpx_check")
+
+
+def test_tensorplay_autograd_reaches_the_new_kernels(cuda):
+    """oracle/_ref/tpx_check (built by oracle/build_tpx_check.sh): TensorPlay's own autograd engine on CUDA
+    tensors -- SumBackward, MeanBackward, VarBackward (whose formula calls mean()) and AccumulateGrad's
+    un-broadcasting ops::sum(grad, dims, false) -- with the reference's reduction kernels absent from
+    the link, so every reduction comes from this repository; gradients are checked against their
+    closed forms and the adapter's call counter shows where they were computed."""
+    if not os.path.exists(TPX_BIN):
+        pytest.skip("tpx_check was not built (needs a TensorPlay checkout at build time)")
+    r = subprocess.run([TPX_BIN], capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "0 failures" in r.stdout
