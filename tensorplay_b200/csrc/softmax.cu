@@ -5,15 +5,17 @@
 //   m = max over the dim (the reduction kernels' rule: NaN is never the maximum),
 //   e = exp(x - m),  s = sum e,  softmax = e / s,  log_softmax = (x - m) - log s
 // with no special cases, so rows holding NaN, +inf or only -inf come out as NaN exactly where the
-// reference's chain of float operations produces NaN.  exp and the quotient are float32; the sum is
-// kept per thread in float32 over a few hundred terms and merged in float64.
+// reference's chain of float operations produces NaN.  exp is float32 (hardware ex2), the quotient a
+// multiplication by the reciprocal of the sum; the sum is kept per thread in float32 over a few
+// hundred terms and merged in float64.  Results are held to 1e-5 relative of a float64 evaluation.
 //
 //   dim is the last, contiguous dim ("rows"):
 //     softmax_warp_kernel   one warp per row, the row in registers            (rows of up to 1024)
 //     softmax_long_kernel   S CTAs per row (a cluster when S > 1): every thread keeps a running
 //                           (max, sum) pair over its part, the CTA's pair goes to every CTA of the
 //                           row through distributed shared memory, one cluster barrier, and the second
-//                           sweep over the CTA's slice -- still in L2 -- writes the result
+//                           sweep writes the result from the CTA's slice, which stayed in shared memory
+//                           (slices of up to 24 K elements; longer ones are read again, from L2 at best)
 //   any other dim of a contiguous tensor, viewed as [outer, C, inner]:
 //     softmax_col_kernel    a thread per (outer, inner) column, coalesced along inner, two sweeps
 #include "common.cuh"
@@ -27,6 +29,12 @@ namespace tpb {
 
 namespace cg = cooperative_groups;
 
+// exp on the hot path: ex2.approx of x * log2(e) (two instructions; the library expf and a float
+// division per element made the kernels compute-bound: [4096,4096] took 57-61 us with them).  Relative
+// error about 2^-22 plus 2^-24 * |x| from the rounded product: below 3e-6 for |x| < 88, inside the 1e-5
+// that the results are held to.  exp(-inf) = 0 and exp(NaN) = NaN as with expf.
+__device__ __forceinline__ float fast_exp(float x) { return __expf(x); }
+
 // Running (max, sum of exp(x - max)) of a set of values; the empty set is (-inf, 0).
 struct MaxSum {
     float m, s;
@@ -35,46 +43,39 @@ struct MaxSum {
     __device__ __forceinline__ void add4(float a, float b, float c, float d) {
         // the reference's max scan skips NaN (strict compare); fmaxf does the same
         const float cm = fmaxf(fmaxf(a, b), fmaxf(c, d));
-        if (cm > m) { s *= expf(m - cm); m = cm; }   // m = -inf, s = 0 at the start: 0 * exp(-inf) = 0
+        if (cm > m) { s *= fast_exp(m - cm); m = cm; }   // m = -inf, s = 0 at the start: 0 * exp(-inf) = 0
         if (m == -INFINITY) {
             // nothing but -inf (and maybe NaN) so far: -inf adds nothing once the row's maximum is known
             // (exp(-inf - max) = 0); only a NaN must not be lost
             if (a != a || b != b || c != c || d != d) s = NAN;
             return;
         }
-        s += (expf(a - m) + expf(b - m)) + (expf(c - m) + expf(d - m));
+        s += (fast_exp(a - m) + fast_exp(b - m)) + (fast_exp(c - m) + fast_exp(d - m));
     }
     __device__ __forceinline__ void add(float a) {
-        if (a > m) { s *= expf(m - a); m = a; }
+        if (a > m) { s *= fast_exp(m - a); m = a; }
         if (m == -INFINITY) { if (a != a) s = NAN; return; }
-        s += expf(a - m);
+        s += fast_exp(a - m);
     }
 };
 
-// Merge in float64: (m, s) pairs of lanes, warps, CTAs.  NaN sums propagate; a part that saw
-// nothing (m = -inf, s = 0) leaves the other unchanged.
-struct MaxSum64 {
-    float m;
-    double s;
-    __device__ __forceinline__ void merge(float om, double os) {
-        if (om > m) { s = s * exp((double)m - (double)om) + os; m = om; }
-        else if (om == m) { s += os; }
-        else { s += os * exp((double)om - (double)m); }
-    }
-};
-
-__device__ __forceinline__ MaxSum64 warp_merge(float m, double s) {
-    MaxSum64 r{m, s};
+// Merging the threads' (m, s) pairs: the maximum first (shuffles of one float), then every thread
+// brings its sum to that maximum with ONE exp, then the sums are added in float64.  (A tree of pairwise
+// merges with an exp at every level put ten dependent float64 exps behind every row.)
+//   m = -inf  the thread saw nothing that counts: its s (0, or NaN if it saw a NaN) passes unscaled
+//   M = +inf  exp(inf - inf) = NaN, as in the reference's chain
+__device__ __forceinline__ float warp_max(float m) {
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-        const float om = __shfl_xor_sync(kFull, r.m, d);
-        const double os = __shfl_xor_sync(kFull, r.s, d);
-        // both partners must end up with the same pair: merge symmetrically
-        MaxSum64 t = r;
-        t.merge(om, os);
-        r = t;
-    }
-    return r;
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, d));
+    return m;
+}
+__device__ __forceinline__ double warp_sum(double s) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(kFull, s, d);
+    return s;
+}
+__device__ __forceinline__ double rescaled(float m, double s, float M) {
+    return m == -INFINITY ? s : s * (double)expf(m - M);
 }
 
 // ---------------------------------------------------------------- one warp per row ----------
@@ -107,16 +108,16 @@ softmax_warp_kernel(const float* __restrict__ in, float* __restrict__ out, long 
     for (int u = 0; u < VPL; ++u) {
         if ((u * 32 + lane) * 4 < len) acc.add4(v[u].x, v[u].y, v[u].z, v[u].w);   // padding is -inf: exp gives 0
     }
-    const MaxSum64 t = warp_merge(acc.m, (double)acc.s);
-    const float m = t.m, s = (float)t.s;
-    const float log_s = logf(s);
+    const float m = warp_max(acc.m);
+    const float s = (float)warp_sum(rescaled(acc.m, (double)acc.s, m));
+    const float log_s = logf(s), inv_s = 1.0f / s;
 #pragma unroll
     for (int u = 0; u < VPL; ++u) {
         const int e0 = (u * 32 + lane) * 4;
-        const float o0 = LOG ? (v[u].x - m) - log_s : expf(v[u].x - m) / s;
-        const float o1 = LOG ? (v[u].y - m) - log_s : expf(v[u].y - m) / s;
-        const float o2 = LOG ? (v[u].z - m) - log_s : expf(v[u].z - m) / s;
-        const float o3 = LOG ? (v[u].w - m) - log_s : expf(v[u].w - m) / s;
+        const float o0 = LOG ? (v[u].x - m) - log_s : fast_exp(v[u].x - m) * inv_s;
+        const float o1 = LOG ? (v[u].y - m) - log_s : fast_exp(v[u].y - m) * inv_s;
+        const float o2 = LOG ? (v[u].z - m) - log_s : fast_exp(v[u].z - m) * inv_s;
+        const float o3 = LOG ? (v[u].w - m) - log_s : fast_exp(v[u].w - m) * inv_s;
         if (vec && e0 + 3 < len) {
             *reinterpret_cast<float4*>(q + e0) = make_float4(o0, o1, o2, o3);
         } else {
@@ -135,14 +136,16 @@ struct LongShared {
     double wsum[32];
     float cm[8];      // (max, sum) of every CTA of the row, written by those CTAs
     double cs[8];
-    float m;
-    float s;
 };
 
-template <bool LOG>
+// STAGE: the CTA's slice is kept in dynamic shared memory between the two sweeps (the vectorised path
+// only, slices of at most 24 K elements), so the input is read from memory exactly once; otherwise the
+// second sweep reads it again and relies on L2.
+template <bool LOG, bool STAGE>
 __global__ void __launch_bounds__(512, 2)
 softmax_long_kernel(const float* __restrict__ in, float* __restrict__ out, long long k1, long long ks0,
                     long long ks1, long long len, long long chunk, int S, int vec) {
+    extern __shared__ __align__(16) float stage[];
     __shared__ LongShared sh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
     cg::cluster_group cluster = cg::this_cluster();
@@ -166,63 +169,58 @@ softmax_long_kernel(const float* __restrict__ in, float* __restrict__ out, long 
         for (; i + 3LL * nthr < nvec; i += 4LL * nthr) {
             float4 v[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ld_keep4(p + ((i + (long long)u * nthr) << 2));
+            for (int u = 0; u < 4; ++u) v[u] = STAGE ? ld_stream4(p + ((i + (long long)u * nthr) << 2)) : ld_keep4(p + ((i + (long long)u * nthr) << 2));
 #pragma unroll
-            for (int u = 0; u < 4; ++u) acc.add4(v[u].x, v[u].y, v[u].z, v[u].w);
+            for (int u = 0; u < 4; ++u) {
+                if (STAGE) reinterpret_cast<float4*>(stage)[i + (long long)u * nthr] = v[u];
+                acc.add4(v[u].x, v[u].y, v[u].z, v[u].w);
+            }
         }
         for (; i < nvec; i += nthr) {
-            const float4 v = ld_keep4(p + (i << 2));
+            const float4 v = STAGE ? ld_stream4(p + (i << 2)) : ld_keep4(p + (i << 2));
+            if (STAGE) reinterpret_cast<float4*>(stage)[i] = v;
             acc.add4(v.x, v.y, v.z, v.w);
         }
         for (long long j = (nvec << 2) + tid; j < n; j += nthr) acc.add(p[j]);
     }
-    // ---- CTA pair, then the row's pair
-    MaxSum64 t = warp_merge(acc.m, (double)acc.s);
-    if (lane == 0) { sh.wm[warp] = t.m; sh.wsum[warp] = t.s; }
+    // ---- the CTA's pair (every thread ends up with it), then the row's pair
+    const int nw = nthr >> 5;
+    const float wmx = warp_max(acc.m);
+    if (lane == 0) sh.wm[warp] = wmx;
     __syncthreads();
-    if (warp == 0) {
-        const int nw = nthr >> 5;
-        MaxSum64 u = warp_merge(lane < nw ? sh.wm[lane] : -INFINITY, lane < nw ? sh.wsum[lane] : 0.0);
-        if (lane == 0) {
-            if (S > 1) {
-                for (int j = 0; j < S; ++j) {   // this CTA's pair into every CTA of the row
-                    *cluster.map_shared_rank(&sh.cm[c], (unsigned)j) = u.m;
-                    *cluster.map_shared_rank(&sh.cs[c], (unsigned)j) = u.s;
-                }
-            } else {
-                sh.m = u.m;
-                sh.s = (float)u.s;
-            }
-        }
-    }
+    float m = warp_max(lane < nw ? sh.wm[lane] : -INFINITY);
+    const double wsm = warp_sum(rescaled(acc.m, (double)acc.s, m));
+    if (lane == 0) sh.wsum[warp] = wsm;
+    __syncthreads();
+    double sd = warp_sum(lane < nw ? sh.wsum[lane] : 0.0);
     if (S > 1) {
-        cluster.sync();
-        if (tid == 0) {
-            MaxSum64 u{sh.cm[0], sh.cs[0]};
-            for (int j = 1; j < S; ++j) u.merge(sh.cm[j], sh.cs[j]);   // the same order in every CTA
-            sh.m = u.m;
-            sh.s = (float)u.s;
+        if (tid < S) {   // this CTA's pair into every CTA of the row
+            *cluster.map_shared_rank(&sh.cm[c], (unsigned)tid) = m;
+            *cluster.map_shared_rank(&sh.cs[c], (unsigned)tid) = sd;
         }
+        cluster.sync();
+        const float cm = lane < S ? sh.cm[lane] : -INFINITY;
+        m = warp_max(cm);
+        sd = warp_sum(lane < S ? rescaled(cm, sh.cs[lane], m) : 0.0);   // the same order in every CTA
     }
-    __syncthreads();
-    const float m = sh.m, s = sh.s;
-    const float log_s = logf(s);
+    const float s = (float)sd;
+    const float log_s = logf(s), inv_s = 1.0f / s;
 
     // ---- sweep 2: the slice again (L2), result out
     {
         long long i = tid;
         for (; i < nvec; i += nthr) {
-            const float4 v = ld_stream4(p + (i << 2));
+            const float4 v = STAGE ? reinterpret_cast<const float4*>(stage)[i] : ld_stream4(p + (i << 2));
             float4 o;
-            o.x = LOG ? (v.x - m) - log_s : expf(v.x - m) / s;
-            o.y = LOG ? (v.y - m) - log_s : expf(v.y - m) / s;
-            o.z = LOG ? (v.z - m) - log_s : expf(v.z - m) / s;
-            o.w = LOG ? (v.w - m) - log_s : expf(v.w - m) / s;
+            o.x = LOG ? (v.x - m) - log_s : fast_exp(v.x - m) * inv_s;
+            o.y = LOG ? (v.y - m) - log_s : fast_exp(v.y - m) * inv_s;
+            o.z = LOG ? (v.z - m) - log_s : fast_exp(v.z - m) * inv_s;
+            o.w = LOG ? (v.w - m) - log_s : fast_exp(v.w - m) * inv_s;
             *reinterpret_cast<float4*>(q + (i << 2)) = o;
         }
         for (long long j = (nvec << 2) + tid; j < n; j += nthr) {
             const float x = p[j];
-            q[j] = LOG ? (x - m) - log_s : expf(x - m) / s;
+            q[j] = LOG ? (x - m) - log_s : fast_exp(x - m) * inv_s;
         }
     }
     // a CTA must not leave while the others may still write their pair into its shared memory:
@@ -248,10 +246,10 @@ softmax_col_kernel(const float* __restrict__ in, float* __restrict__ out, long l
         acc.add4(x0, x1, x2, x3);
     }
     for (; j < C; ++j) acc.add(p[j * inner]);
-    const float m = acc.m, s = acc.s, log_s = logf(acc.s);
+    const float m = acc.m, log_s = logf(acc.s), inv_s = 1.0f / acc.s;
     for (j = 0; j < C; ++j) {
         const float x = p[j * inner];
-        q[j * inner] = LOG ? (x - m) - log_s : expf(x - m) / s;
+        q[j * inner] = LOG ? (x - m) - log_s : fast_exp(x - m) * inv_s;
     }
 }
 
@@ -322,20 +320,35 @@ extern "C" int tpb200_softmax(int log, const void* in, int dtype, int ndim, cons
 #undef TPB_SM_WARP
             return TPB200_OK;
         }
-        // S CTAs per row: a cluster of 2, 4 or 8 where the rows alone leave the GPU partly empty and a
-        // slice still holds 32 K elements
-        const int sms = sm_count();
+        // Rows of up to 48 K elements: one or two CTAs per row, each keeping its slice (at most 24 K
+        // elements, 96 KB: two CTAs per SM) in shared memory between the sweeps, so the input is read
+        // once.  Longer rows: the second sweep reads the slice again, and S only has to give the GPU
+        // enough CTAs (two per SM).  Measured on [256,151936] (algorithmic 311 MB): S = 8 with staged
+        // slices 84 us -- seven waves of CTAs that each load, wait for their cluster and only then
+        // store; S = 1 / 2 / 4 without staging 80 / 74 / 77 us.
+        constexpr long long kStageMax = 24 * 1024;
         int S = 1;
-        while (S < 8 && rows * (2LL * S) <= 2LL * sms && C / (2LL * S) >= 32 * 1024) S *= 2;
+        if (C > kStageMax && C <= 2 * kStageMax) S = 2;
+        else if (C > 2 * kStageMax)
+            while (S < 8 && rows * S < 2LL * sm_count() && ceil_div(C, 2 * S) >= 16384) S *= 2;
         int fs = 0;
         if (env_int("TPB200_SOFTMAX_SLICES", &fs) && (fs == 1 || fs == 2 || fs == 4 || fs == 8)) S = fs;
         const long long chunk = round_up(ceil_div(C, S), 4);
         if (rows * S > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
         const int threads = C / S >= 8192 ? 512 : (C / S >= 2048 ? 256 : 128);
         const dim3 grid((unsigned)(rows * S));
-        cudaError_t e;
-        if (log) e = launch_ex(softmax_long_kernel<true>, grid, threads, 0, st, S, false, x, y, k1, ks0, ks1, C, chunk, S, vec);
-        else     e = launch_ex(softmax_long_kernel<false>, grid, threads, 0, st, S, false, x, y, k1, ks0, ks1, C, chunk, S, vec);
+        const bool stage = vec && chunk <= kStageMax;
+        const size_t smem = stage ? (size_t)chunk * sizeof(float) : 0;
+        cudaError_t e = cudaSuccess;
+#define TPB_SM_LONG(LOGV, STAGEV)                                                                                  \
+    do {                                                                                                           \
+        if (smem + 8192 > 48 * 1024)                                                                               \
+            TPB_CUDA_OK(cudaFuncSetAttribute(softmax_long_kernel<LOGV, STAGEV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        e = launch_ex(softmax_long_kernel<LOGV, STAGEV>, grid, threads, smem, st, S, false, x, y, k1, ks0, ks1, C, chunk, S, vec);        \
+    } while (0)
+        if (log) { if (stage) TPB_SM_LONG(true, true); else TPB_SM_LONG(true, false); }
+        else     { if (stage) TPB_SM_LONG(false, true); else TPB_SM_LONG(false, false); }
+#undef TPB_SM_LONG
         if (e != cudaSuccess) return cuda_fail(e, "softmax_long_kernel");
         return TPB200_OK;
     }
