@@ -302,10 +302,30 @@ int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int64_t n, int6
  * kernel whose wait gave up sets a per-device status word; a top-k kernel then leaves its outputs
  * unwritten, the fused exchange writes NaN / -1 so that a timed-out call cannot pass for a result.
  * Status values: 0 no wait ever gave up; 1..4, 6..8 a top-k wait (which one is in the low byte);
- * 5 the peer exchange.  This call SYNCHRONISES with the device, returns the word in *status_out and
- * clears it.  No reference counterpart.
+ * 5 the peer exchange; 0x40000000 a range violation in a checked build (below).  This call
+ * SYNCHRONISES with the device, returns the word in *status_out and clears it.  No reference
+ * counterpart.
  */
 int tpb200_device_status(int* status_out);
+
+/* ---- checked build ----------------------------------------------------------------------------
+ * libtpb200_checked.so is the same library compiled with -DTPB200_CHECKED: every entry point first
+ * registers the address ranges its kernels may touch (the input view, the outputs, the workspace,
+ * exchange buffers), and every access of a kernel to global memory is compared with them.  An
+ * access outside the ranges is not made (it is turned to a sink buffer), the first one is recorded
+ * and all are counted; nothing traps and the context stays usable.  It is the stand-in for a memory
+ * checker, several times slower than the ordinary build, one call at a time per device.
+ *
+ * tpb200_check_report fills info[0..5] = {1 in a checked build else 0, violations since the last
+ * report, source file id of the first (1 reduce, 2 top-k, 3 top-k select, 4 softmax, 5 median,
+ * 6 copy, 0 shared header), its line, its address, its size in bytes}, SYNCHRONISES and clears the
+ * record.  tpb200_check_trim_next(bytes) is the checker's own test: the next entry point registers
+ * every range `bytes` shorter at its end, so that correct kernels are seen to be caught and skipped;
+ * TPB200_ERR_UNSUPPORTED in the ordinary build.  No reference counterpart.
+ */
+#define TPB200_CHECK_INFO_FIELDS 6
+int tpb200_check_report(int64_t* info, int n_info);
+int tpb200_check_trim_next(int64_t bytes);
 
 #ifdef __cplusplus
 }

@@ -9,7 +9,10 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libtpb200.so")
+# TPB200_CHECKED=1 in the environment selects the range-checking build of the same sources
+# (libtpb200_checked.so: see "checked build" in include/tpb200.h); it must exist, nothing falls back.
+CHECKED = os.environ.get("TPB200_CHECKED", "") not in ("", "0")
+LIB_PATH = os.path.join(_PKG, "libtpb200_checked.so" if CHECKED else "libtpb200.so")
 
 # error codes of include/tpb200.h
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_DIM_RANGE, ERR_EMPTY, ERR_WORKSPACE, ERR_CUDA = range(7)
@@ -25,7 +28,7 @@ SYMBOLS = [
     "tpb200_last_error", "tpb200_version", "tpb200_reduce", "tpb200_reduce_workspace_bytes",
     "tpb200_topk", "tpb200_topk_workspace_bytes", "tpb200_reduce_partial",
     "tpb200_reduce_partial_workspace_bytes", "tpb200_reduce_combine", "tpb200_topk_merge",
-    "tpb200_device_status", "tpb200_reduce_all_noalloc", "tpb200_exchange_buffer_bytes",
+    "tpb200_device_status", "tpb200_check_report", "tpb200_check_trim_next", "tpb200_reduce_all_noalloc", "tpb200_exchange_buffer_bytes",
     "tpb200_reduce_fused_exchange", "tpb200_topk_plan_info", "tpb200_set_exchange_wait_polls",
     "tpb200_softmax", "tpb200_median", "tpb200_median_workspace_bytes",
     "tpb200_comm_create", "tpb200_comm_destroy", "tpb200_comm_size", "tpb200_comm_fused", "tpb200_comm_stream",
@@ -51,7 +54,7 @@ def lib() -> ctypes.CDLL:
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m tensorplay_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python -m tensorplay_b200.build{' --checked' if CHECKED else ''}` "
             "(needs nvcc; there is no CPU or PyTorch fallback)")
     L = ctypes.CDLL(LIB_PATH)
     vp, i, i64, u64, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64, ctypes.c_size_t
@@ -59,6 +62,10 @@ def lib() -> ctypes.CDLL:
     L.tpb200_last_error.argtypes = []
     L.tpb200_version.restype = i
     L.tpb200_version.argtypes = []
+    L.tpb200_check_report.restype = i
+    L.tpb200_check_report.argtypes = [_I64P, i]
+    L.tpb200_check_trim_next.restype = i
+    L.tpb200_check_trim_next.argtypes = [i64]
     L.tpb200_reduce.restype = i
     L.tpb200_reduce.argtypes = [i, vp, i, i, _I64P, _I64P, u64, i, i64, vp, vp, vp, sz, vp]
     L.tpb200_reduce_workspace_bytes.restype = sz
@@ -146,6 +153,24 @@ def topk_plan_info(sizes, strides, dim: int, k: int) -> dict:
     check(lib().tpb200_topk_plan_info(F32, len(sizes), i64_array(list(sizes)), i64_array(list(strides)), dim, k,
                                       info, len(PLAN_FIELDS)))
     return dict(zip(PLAN_FIELDS, [int(v) for v in info]))
+
+
+CHECK_INFO = ("checked_build", "violations", "file", "line", "address", "bytes")
+
+
+def check_report() -> dict:
+    """Synchronise and return (then clear) the checked build's record: how many accesses fell outside
+    the ranges registered for their call, and where the first one was (file id, line, address, size).
+    In the ordinary build "checked_build" is 0 and the rest is zero."""
+    info = (ctypes.c_int64 * len(CHECK_INFO))()
+    check(lib().tpb200_check_report(info, len(CHECK_INFO)))
+    return dict(zip(CHECK_INFO, (int(v) for v in info)))
+
+
+def check_trim_next(nbytes: int) -> None:
+    """The checker's own test (checked build only): the next call registers every range `nbytes`
+    shorter at its end."""
+    check(lib().tpb200_check_trim_next(int(nbytes)))
 
 
 def device_status() -> int:

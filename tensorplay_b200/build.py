@@ -14,6 +14,9 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_PKG, "csrc")
 _ROOT = os.path.dirname(_PKG)
 LIB_PATH = os.path.join(_PKG, "libtpb200.so")
+# The same sources with -DTPB200_CHECKED: every global access range-checked (see include/tpb200.h).
+# Relocatable device code, because the range table and the violation record are shared by all files.
+LIB_PATH_CHECKED = os.path.join(_PKG, "libtpb200_checked.so")
 
 SOURCES = ["api_common.cu", "reduce.cu", "topk.cu", "softmax.cu", "median.cu", "comm.cu", "copy.cu"]
 NVCC_FLAGS = [
@@ -30,27 +33,32 @@ def _nvcc() -> str:
     return exe
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def _stale(lib: str = LIB_PATH) -> bool:
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB_PATH)
+    t = os.path.getmtime(lib)
     deps = [os.path.join(_CSRC, f) for f in os.listdir(_CSRC)]
     deps.append(os.path.join(_ROOT, "include", "tpb200.h"))
     return any(os.path.getmtime(d) > t for d in deps if os.path.isfile(d))
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    """Build libtpb200.so if it is missing or older than its sources; returns its path."""
-    if not force and not _stale():
-        return LIB_PATH
+def build_library(force: bool = False, verbose: bool = False, checked: bool = False) -> str:
+    """Build libtpb200.so (or, with checked=True, libtpb200_checked.so) if it is missing or older than
+    its sources; returns its path."""
+    lib = LIB_PATH_CHECKED if checked else LIB_PATH
+    if not force and not _stale(lib):
+        return lib
     nvcc = _nvcc()
-    objdir = os.path.join(_PKG, "build")
+    # separately compiled device functions do not see their callers' launch bounds: one register cap for all
+    # (40: the tightest launch bound in the sources, 512 threads x 3 CTAs per SM)
+    extra = ["-DTPB200_CHECKED", "-rdc=true", "-maxrregcount=40"] if checked else []
+    objdir = os.path.join(_PKG, "build_checked" if checked else "build")
     os.makedirs(objdir, exist_ok=True)
     srcs = [s for s in SOURCES if os.path.exists(os.path.join(_CSRC, s))]
 
     def compile_one(src: str) -> str:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(_CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(_CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -62,14 +70,14 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=len(srcs)) as ex:
         objs = list(ex.map(compile_one, srcs))
-    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd = [nvcc, "-shared", "-o", lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_PATH
+    return lib
 
 
 if __name__ == "__main__":
     import sys
 
-    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--checked" in sys.argv))

@@ -1,5 +1,6 @@
 // Process-wide pieces of the C ABI: the per-thread error message, the library version and the
 // cached SM count that the planners size their grids with.
+#include "common.cuh"
 #include "host_util.h"
 
 #include <mutex>
@@ -55,7 +56,82 @@ int* device_status_word() {
     return cached[dev];
 }
 
+#ifdef TPB200_CHECKED
+// ---- checked build: the range table, the record of the first violation, the sink
+__device__ CheckTable g_check_table;
+__device__ CheckRecord g_check_record;
+__device__ __align__(16) unsigned char g_check_sink[256];
+
+__device__ __noinline__ const void* check_access(const void* p, unsigned bytes, int file, int line) {
+    const unsigned long long a = (unsigned long long)p;
+    const int n = g_check_table.n;
+    for (int i = 0; i < n; ++i)
+        if (a >= g_check_table.r[i].lo && a + bytes <= g_check_table.r[i].hi) return p;
+    if (atomicCAS(&g_check_record.hit, 0, 1) == 0) {
+        g_check_record.file = file;
+        g_check_record.line = line;
+        g_check_record.bytes = bytes;
+        g_check_record.addr = a;
+    }
+    atomicAdd(&g_check_record.count, 1ull);
+    atomicMax(&g_device_status, kErrChecked);
+    return g_check_sink;   // the access goes here instead
+}
+
+__global__ void check_set_kernel(CheckTable t) { g_check_table = t; }
+
+static long long g_trim_next = 0;
+
+int check_register(cudaStream_t st, const HostRange* r, int n) {
+    CheckTable t{};
+    if (n > kCheckRanges) return fail(TPB200_ERR_INVALID, "checked build: more than %d ranges in one call", kCheckRanges);
+    const long long trim = g_trim_next;
+    g_trim_next = 0;
+    for (int i = 0; i < n; ++i) {
+        if (!r[i].p || r[i].bytes == 0) continue;
+        const unsigned long long lo = (unsigned long long)r[i].p;
+        unsigned long long hi = lo + r[i].bytes;
+        if (trim > 0) hi = hi - lo > (unsigned long long)trim ? hi - (unsigned long long)trim : lo;
+        t.r[t.n].lo = lo;
+        t.r[t.n].hi = hi;
+        ++t.n;
+    }
+    check_set_kernel<<<1, 1, 0, st>>>(t);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "check_set_kernel");
+    return TPB200_OK;
+}
+#endif
+
 }  // namespace tpb
+
+extern "C" int tpb200_check_report(int64_t* info, int n_info) {
+    if (!info || n_info < TPB200_CHECK_INFO_FIELDS) return tpb::fail(TPB200_ERR_INVALID, "info must hold %d fields", TPB200_CHECK_INFO_FIELDS);
+    for (int i = 0; i < n_info; ++i) info[i] = 0;
+#ifdef TPB200_CHECKED
+    tpb::CheckRecord rec{}, zero{};
+    TPB_CUDA_OK(cudaMemcpyFromSymbol(&rec, tpb::g_check_record, sizeof(rec)));
+    if (rec.hit || rec.count) TPB_CUDA_OK(cudaMemcpyToSymbol(tpb::g_check_record, &zero, sizeof(zero)));
+    info[0] = 1;
+    info[1] = (int64_t)rec.count;
+    info[2] = rec.file;
+    info[3] = rec.line;
+    info[4] = (int64_t)rec.addr;
+    info[5] = rec.bytes;
+#endif
+    return TPB200_OK;
+}
+
+extern "C" int tpb200_check_trim_next(int64_t bytes) {
+#ifdef TPB200_CHECKED
+    if (bytes < 0) return tpb::fail(TPB200_ERR_INVALID, "bytes must not be negative");
+    tpb::g_trim_next = bytes;
+    return TPB200_OK;
+#else
+    (void)bytes;
+    return tpb::fail(TPB200_ERR_UNSUPPORTED, "this library was built without -DTPB200_CHECKED");
+#endif
+}
 
 extern "C" int tpb200_device_status(int* status_out) {
     if (!status_out) return tpb::fail(TPB200_ERR_INVALID, "status_out is NULL");

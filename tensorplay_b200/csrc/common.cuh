@@ -16,9 +16,41 @@ constexpr unsigned kFull = 0xffffffffu;
 // "no element selected yet" index: larger than any real position, so a real tie always wins.
 constexpr long long kNoIndex = 0x7fffffffffffffffLL;
 
+// ------------------------------------------------------------------ checked build ----------
+// With -DTPB200_CHECKED (the library libtpb200_checked.so) every access to global memory goes through
+// TPB_CK / TPB_CKN: the address range is compared with the ranges that the host entry point registered
+// for its call (input view, outputs, workspace, exchange buffers).  An access outside them is NOT
+// made: it is turned to a small sink buffer, the first one is recorded (file id, line, address, size)
+// and counted, and the per-device status word becomes kErrChecked.  Nothing traps.  This is the
+// stand-in for a memory checker on machines where none can be run; the ordinary build compiles the
+// macros to the bare pointer.
+constexpr int kErrChecked = 0x40000000;   // above every wait code, so atomicMax keeps it
+#ifdef TPB200_CHECKED
+constexpr int kCheckRanges = 24;
+struct CheckRange { unsigned long long lo, hi; };   // [lo, hi), bytes
+struct CheckTable { CheckRange r[kCheckRanges]; int n; int pad; };
+struct CheckRecord { int hit, file, line; unsigned bytes; unsigned long long addr, count; };
+extern __device__ CheckTable g_check_table;
+extern __device__ CheckRecord g_check_record;
+extern __device__ __align__(16) unsigned char g_check_sink[256];
+__device__ const void* check_access(const void* p, unsigned bytes, int file, int line);
+template <class T>
+__device__ __forceinline__ T* checked(T* p, unsigned bytes, int file, int line) {
+    return (T*)check_access((const void*)p, bytes, file, line);
+}
+#ifndef TPB_FILE_ID
+#define TPB_FILE_ID 0
+#endif
+#define TPB_CK(p) ::tpb::checked((p), (unsigned)sizeof(*(p)), TPB_FILE_ID, __LINE__)
+#define TPB_CKN(p, bytes) ::tpb::checked((p), (unsigned)(bytes), TPB_FILE_ID, __LINE__)
+#else
+#define TPB_CK(p) (p)
+#define TPB_CKN(p, bytes) (p)
+#endif
+
 // ------------------------------------------------------------------ loads ------------------
 // Input is read exactly once: bypass L1 allocation so the 16-byte sectors stream from L2/HBM.
-__device__ __forceinline__ float4 ld_stream4(const float* p) {
+__device__ __forceinline__ float4 ld_stream4_raw(const float* p) {
     float4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
@@ -27,18 +59,22 @@ __device__ __forceinline__ float4 ld_stream4(const float* p) {
 }
 // The same 128-bit read-only load WITH allocation in L1: for data that the same SM reads again within
 // microseconds (the top-k kernels re-read the few elements that pass their threshold test).
-__device__ __forceinline__ float4 ld_keep4(const float* p) {
+__device__ __forceinline__ float4 ld_keep4_raw(const float* p) {
     float4 v;
     asm volatile("ld.global.nc.v4.f32 {%0,%1,%2,%3}, [%4];"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
                  : "l"(p));
     return v;
 }
-__device__ __forceinline__ float ld_stream1(const float* p) {
+__device__ __forceinline__ float ld_stream1_raw(const float* p) {
     float v;
     asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
     return v;
 }
+// the loads as the kernels spell them (macros, so that a checked build records the caller's line)
+#define ld_stream4(p) ::tpb::ld_stream4_raw(TPB_CKN((p), 16))
+#define ld_keep4(p) ::tpb::ld_keep4_raw(TPB_CKN((p), 16))
+#define ld_stream1(p) ::tpb::ld_stream1_raw(TPB_CKN((p), 4))
 
 // ------------------------------------------------------------------ packed partial ---------
 // One record per (row, slice) between the two passes of a split reduction, and per GPU in the
@@ -275,7 +311,7 @@ struct Epilogue {
 
 __device__ __forceinline__ void write_result(const SumAcc& a, const Epilogue& e, double count, float* ov, long long*, long long o) {
     // mean of an empty reduction is 0/0 = NaN, as in the reference (sum 0 divided by count 0)
-    ov[o] = e.op == TPB200_OP_MEAN ? (float)(a.s / count) : (float)a.s;
+    *TPB_CK(&ov[o]) = e.op == TPB200_OP_MEAN ? (float)(a.s / count) : (float)a.s;
 }
 __device__ __forceinline__ void write_result(const MomAcc& a, const Epilogue& e, double count, float* ov, long long*, long long o) {
     // divisor max(0, n - correction), division in double, one rounding to float
@@ -283,25 +319,25 @@ __device__ __forceinline__ void write_result(const MomAcc& a, const Epilogue& e,
     double dv = count - (double)e.correction;
     if (dv < 0.0) dv = 0.0;
     float var = count == 0.0 ? NAN : (float)(a.m2 / dv);
-    ov[o] = e.op == TPB200_OP_STD ? sqrtf(var) : var;
+    *TPB_CK(&ov[o]) = e.op == TPB200_OP_STD ? sqrtf(var) : var;
 }
 template <int F>
 __device__ __forceinline__ void write_result(const PowSumAcc<F>& a, const Epilogue&, double, float* ov, long long*, long long o) {
-    ov[o] = F == 0 ? (float)a.s : (float)sqrt(a.s);
+    *TPB_CK(&ov[o]) = F == 0 ? (float)a.s : (float)sqrt(a.s);
 }
 __device__ __forceinline__ void write_result(const ProdAcc& a, const Epilogue&, double, float* ov, long long*, long long o) {
-    ov[o] = (float)a.p;
+    *TPB_CK(&ov[o]) = (float)a.p;
 }
 template <bool IS_ALL>
 __device__ __forceinline__ void write_result(const BoolAcc<IS_ALL>& a, const Epilogue&, double, float* ov, long long*, long long o) {
-    reinterpret_cast<unsigned char*>(ov)[o] = (unsigned char)a.f;   // Bool output: one byte per element
+    *TPB_CK(&reinterpret_cast<unsigned char*>(ov)[o]) = (unsigned char)a.f;   // Bool output: one byte per element
 }
 template <bool IS_MAX, bool ABS>
 __device__ __forceinline__ void write_result(const ExtAcc<IS_MAX, ABS>& a, const Epilogue& e, double, float* ov, long long* oi, long long o) {
     // nothing compared better (empty, all NaN, or all equal to the start value): index 0 and the
     // start value, as in the reference's scan (ReductionKernels.cpp:692-694, 727-735)
-    if (ov) ov[o] = a.v;
-    if (oi) oi[o] = a.i == kNoIndex ? 0 : a.i;
+    if (ov) *TPB_CK(&ov[o]) = a.v;
+    if (oi) *TPB_CK(&oi[o]) = a.i == kNoIndex ? 0 : a.i;
     (void)e;
 }
 

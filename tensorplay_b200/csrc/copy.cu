@@ -12,6 +12,7 @@
 //            memory, read along the source's unit-stride dim, written along the destination's, both
 //            coalesced; the other dims are decoded once per tile
 //   generic  one element per thread with the div/mod walk, for whatever is left (no unit stride)
+#define TPB_FILE_ID 6
 #include "common.cuh"
 #include "host_util.h"
 
@@ -49,17 +50,17 @@ copy_rows_kernel(unsigned* __restrict__ dst, const unsigned* __restrict__ src, C
             for (int u = 0; u < 4; ++u) {
                 const long long e = e0 + ((long long)u * 256 + threadIdx.x) * 4;
                 if (e + 3 < len) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(s + e);
-                    *reinterpret_cast<uint4*>(t + e) = v;
+                    const uint4 v = *reinterpret_cast<const uint4*>(TPB_CKN(s + e, 16));
+                    *reinterpret_cast<uint4*>(TPB_CKN(t + e, 16)) = v;
                 } else {
-                    for (long long q = e; q < len && q < e + 4; ++q) t[q] = s[q];
+                    for (long long q = e; q < len && q < e + 4; ++q) *TPB_CK(&t[q]) = *TPB_CK(&s[q]);
                 }
             }
         } else {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const long long e = e0 + (long long)u * 256 + threadIdx.x;
-                if (e < len) t[e] = s[e];
+                if (e < len) *TPB_CK(&t[e]) = *TPB_CK(&s[e]);
             }
         }
     }
@@ -94,7 +95,7 @@ copy_tiles_kernel(unsigned* __restrict__ dst, const unsigned* __restrict__ src, 
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const long long b = b0 + ty + 4 * j;
-                v[j] = (a < g.size[A] && b < g.size[B]) ? p[b * g.ss[B]] : 0u;
+                v[j] = (a < g.size[A] && b < g.size[B]) ? *TPB_CK(&p[b * g.ss[B]]) : 0u;
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) tile[ty + 4 * j][tx] = v[j];
@@ -106,7 +107,7 @@ copy_tiles_kernel(unsigned* __restrict__ dst, const unsigned* __restrict__ src, 
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const long long a = a0 + ty + 4 * j;
-                if (a < g.size[A] && b < g.size[B]) q[a * g.ds[A]] = tile[tx][ty + 4 * j];
+                if (a < g.size[A] && b < g.size[B]) *TPB_CK(&q[a * g.ds[A]]) = tile[tx][ty + 4 * j];
             }
         }
         __syncthreads();
@@ -124,7 +125,7 @@ copy_generic_kernel(unsigned* __restrict__ dst, const unsigned* __restrict__ src
             doff += c * g.ds[d];
             soff += c * g.ss[d];
         }
-        dst[doff] = src[soff];
+        *TPB_CK(&dst[doff]) = *TPB_CK(&src[soff]);
     }
 }
 
@@ -159,6 +160,7 @@ extern "C" int tpb200_strided_copy(void* dst, const int64_t* dst_strides, const 
     if (!dst || !src) return fail(TPB200_ERR_INVALID, "NULL pointer argument");
     if (g.nd == 0) { g.nd = 1; g.size[0] = 1; g.ds[0] = 1; g.ss[0] = 1; }
     cudaStream_t st = (cudaStream_t)stream;
+    TPB_CHECK_RANGES(st, view_range(src, ndim, sizes, src_strides, 4), view_range(dst, ndim, sizes, dst_strides, 4));
     unsigned* d = (unsigned*)dst;
     const unsigned* s = (const unsigned*)src;
     const int sms = sm_count();

@@ -108,6 +108,32 @@ inline cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, int threads, s
         if (e__ != cudaSuccess) return ::tpb::cuda_fail(e__, name);                                               \
     } while (0)
 
+// Checked build (-DTPB200_CHECKED): every entry point registers the address ranges its kernels may
+// touch before it launches them -- a one-thread kernel on the same stream writes the table, so the
+// registration is ordered with the launches and can be captured in a graph.  One table per device:
+// calls on different streams of one device must not overlap in a checked build.
+struct HostRange { const void* p; size_t bytes; };
+inline HostRange view_range(const void* base, int ndim, const int64_t* sizes, const int64_t* strides, size_t elem) {
+    long long lo = 0, hi = 0;
+    for (int i = 0; i < ndim; ++i) {
+        if (sizes[i] == 0) return HostRange{base, 0};
+        const long long span = (long long)(sizes[i] - 1) * (long long)strides[i];
+        if (span < 0) lo += span; else hi += span;
+    }
+    return HostRange{(const char*)base + lo * (long long)elem, (size_t)(hi - lo + 1) * elem};
+}
+#ifdef TPB200_CHECKED
+int check_register(cudaStream_t st, const HostRange* r, int n);
+#define TPB_CHECK_RANGES(st, ...)                                                            \
+    do {                                                                                     \
+        const ::tpb::HostRange r__[] = {__VA_ARGS__};                                        \
+        const int rc__ = ::tpb::check_register((st), r__, (int)(sizeof(r__) / sizeof(r__[0]))); \
+        if (rc__ != TPB200_OK) return rc__;                                                  \
+    } while (0)
+#else
+#define TPB_CHECK_RANGES(st, ...) do { } while (0)
+#endif
+
 inline long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 inline long long round_up(long long a, long long b) { return ceil_div(a, b) * b; }
 inline int pow2_ceil(long long v) {

@@ -11,6 +11,7 @@
 //            prefix, reduces the rank and clears the bins for the next sweep.
 // After the third pick the prefix is the key of the median; its value is written to the output.
 // Everything stays on the stream: the state lives in the caller's workspace.
+#define TPB_FILE_ID 5
 #include "common.cuh"
 #include "host_util.h"
 
@@ -61,7 +62,7 @@ median_hist_kernel(const float* __restrict__ in, long long n, MedGeom g, int pas
     int shift, bits;
     digit_of_pass(pass, &shift, &bits);
     const unsigned mask = (1u << bits) - 1u;
-    const unsigned prefix = st->prefix;
+    const unsigned prefix = *TPB_CK(&st->prefix);
     const int above = shift + bits;             // key >> above must equal the prefix (pass 0: nothing above)
     auto count = [&](float x) {
         const unsigned key = median_key(x);
@@ -102,7 +103,7 @@ median_hist_kernel(const float* __restrict__ in, long long n, MedGeom g, int pas
     __syncthreads();
     for (int i = tid; i < kMedBins; i += kMedThreads) {
         const unsigned c = hist[i];
-        if (c) atomicAdd(&st->hist[i], c);
+        if (c) atomicAdd(TPB_CK(&st->hist[i]), c);
     }
 }
 
@@ -113,7 +114,7 @@ median_pick_kernel(MedianState* st, int pass, float* out) {
     __shared__ int found;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // 2048 bins over 1024 threads: two adjacent bins each
-    const unsigned long long c0 = st->hist[2 * tid], c1 = st->hist[2 * tid + 1];
+    const unsigned long long c0 = *TPB_CK(&st->hist[2 * tid]), c1 = *TPB_CK(&st->hist[2 * tid + 1]);
     unsigned long long incl = c0 + c1;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -126,31 +127,31 @@ median_pick_kernel(MedianState* st, int pass, float* out) {
     unsigned long long before = 0;
     for (int w = 0; w < warp; ++w) before += wsum[w];
     const unsigned long long excl = before + incl - (c0 + c1);   // keys in the bins below 2 * tid
-    const unsigned long long rank = st->rank;
+    const unsigned long long rank = *TPB_CK(&st->rank);
     __syncthreads();
     if (rank >= excl && rank < excl + c0) found = 2 * tid;
     else if (rank >= excl + c0 && rank < excl + c0 + c1) found = 2 * tid + 1;
     __syncthreads();
     const int bin = found;
-    st->hist[2 * tid] = 0u;          // clean for the next sweep (and the next call)
-    st->hist[2 * tid + 1] = 0u;
+    *TPB_CK(&st->hist[2 * tid]) = 0u;          // clean for the next sweep (and the next call)
+    *TPB_CK(&st->hist[2 * tid + 1]) = 0u;
     if (bin >= 0 && (bin >> 1) == tid) {
         const int bits = pass == 2 ? 10 : 11;
-        const unsigned prefix = pass == 0 ? (unsigned)bin : ((st->prefix << bits) | (unsigned)bin);
-        st->prefix = prefix;
-        st->rank = rank - (excl + ((bin & 1) ? c0 : 0ull));
-        if (pass == 2) out[0] = median_value(prefix);
+        const unsigned prefix = pass == 0 ? (unsigned)bin : ((*TPB_CK(&st->prefix) << bits) | (unsigned)bin);
+        *TPB_CK(&st->prefix) = prefix;
+        *TPB_CK(&st->rank) = rank - (excl + ((bin & 1) ? c0 : 0ull));
+        if (pass == 2) *TPB_CK(&out[0]) = median_value(prefix);
     }
 }
 
 __global__ void median_init_kernel(MedianState* st, unsigned long long rank, float* out, int empty) {
     const int tid = threadIdx.x;
-    for (int i = tid; i < kMedBins; i += blockDim.x) st->hist[i] = 0u;
+    for (int i = tid; i < kMedBins; i += blockDim.x) *TPB_CK(&st->hist[i]) = 0u;
     if (tid == 0) {
-        st->rank = rank;
-        st->prefix = 0u;
-        st->pad = 0u;
-        if (empty) out[0] = NAN;   // the reference returns NaN for an empty tensor (ReductionKernels.cpp:877)
+        *TPB_CK(&st->rank) = rank;
+        *TPB_CK(&st->prefix) = 0u;
+        *TPB_CK(&st->pad) = 0u;
+        if (empty) *TPB_CK(&out[0]) = NAN;   // the reference returns NaN for an empty tensor (ReductionKernels.cpp:877)
     }
 }
 
@@ -190,6 +191,7 @@ extern "C" int tpb200_median(const void* in, int dtype, int ndim, const int64_t*
     }
     if (n > 0 && !in) return fail(TPB200_ERR_INVALID, "input pointer is NULL");
     cudaStream_t st = (cudaStream_t)stream;
+    TPB_CHECK_RANGES(st, view_range(in, ndim, sizes, strides, 4), HostRange{out, 4}, HostRange{workspace, sizeof(MedianState)});
     MedianState* state = (MedianState*)workspace;
     float* o = (float*)out;
     const unsigned long long rank = n > 0 ? (unsigned long long)((n - 1) / 2) : 0ull;

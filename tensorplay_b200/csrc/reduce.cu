@@ -19,6 +19,7 @@
 //   GENERIC  anything else (and empty reductions): one warp per output, div/mod addressing
 //
 // All combines run in a fixed order, so results are bit-reproducible run to run.
+#define TPB_FILE_ID 1
 #include "common.cuh"
 #include "host_util.h"
 
@@ -148,7 +149,7 @@ row_split_kernel(const float* __restrict__ in, RowGeom g, long long sub, int S, 
     }
     acc.finish_thread();
     block_combine(acc, sm);
-    if (tid == 0) acc.store(&ws[r * S + s]);
+    if (tid == 0) acc.store(TPB_CK(&ws[r * S + s]));
 }
 
 // Pass 2: one warp per row merges that row's S partials in a fixed order (lane l takes
@@ -166,7 +167,7 @@ finalize_kernel(const Packed* __restrict__ ws, long long rows, int S, double cou
     acc.finish_thread();
     for (int s = lane; s < S; s += 32) {
         Acc o;
-        o.load(&ws[r * S + s]);
+        o.load(TPB_CK(&ws[r * S + s]));
         acc.merge(o);
     }
     warp_combine(acc);
@@ -175,7 +176,7 @@ finalize_kernel(const Packed* __restrict__ ws, long long rows, int S, double cou
             Packed out;
             acc.store(&out);
             if (out.i0 != kNoIndex) out.i0 += idx_offset;
-            packed_out[r] = out;
+            *TPB_CK(&packed_out[r]) = out;
         } else {
             write_result(acc, e, count, ov, oi, r);
         }
@@ -272,7 +273,7 @@ col_kernel(const float* __restrict__ in, long long o_stride, long long L, long l
     if (ty == 0 && active) {
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
-            if (ws) acc[v].store(&ws[(o * S + s) * I + i0 + v]);
+            if (ws) acc[v].store(TPB_CK(&ws[(o * S + s) * I + i0 + v]));
             else write_result(acc[v], e, (double)L, ov, oi, o * I + i0 + v);
         }
     }
@@ -286,10 +287,10 @@ col_finalize_kernel(const Packed* __restrict__ ws, long long O, int S, long long
     if (t >= O * I) return;
     const long long o = t / I, i = t - o * I;
     Acc acc;
-    acc.load(&ws[(o * S) * I + i]);
+    acc.load(TPB_CK(&ws[(o * S) * I + i]));
     for (int s = 1; s < S; ++s) {
         Acc b;
-        b.load(&ws[(o * S + s) * I + i]);
+        b.load(TPB_CK(&ws[(o * S + s) * I + i]));
         acc.merge(b);
     }
     write_result(acc, e, count, ov, oi, t);
@@ -635,6 +636,9 @@ extern "C" int tpb200_reduce(int op, const void* in, int dtype, int ndim, const 
     long long* oi = wants_idx ? (long long*)out_idx : nullptr;
     cudaStream_t st = (cudaStream_t)stream;
     const float* x = (const float*)in;
+    TPB_CHECK_RANGES(st, view_range(in, ndim, sizes, strides, 4),
+                     HostRange{ov, (size_t)pl.outs * ((fam == FAM_ALL || fam == FAM_ANY) ? 1 : 4)},
+                     HostRange{oi, (size_t)pl.outs * 8}, HostRange{workspace, pl.ws_bytes});
     switch (fam) {
         case FAM_SUM: return launch_plan<SumAcc>(pl, x, e, ov, oi, workspace, st);
         case FAM_MOM: return launch_plan<MomAcc>(pl, x, e, ov, oi, workspace, st);
@@ -714,6 +718,7 @@ extern "C" int tpb200_reduce_partial(int family, const void* in, int dtype, int6
     cudaStream_t st = (cudaStream_t)stream;
     const float* x = (const float*)in;
     Packed* out = (Packed*)partial_out;
+    TPB_CHECK_RANGES(st, HostRange{in, (size_t)n * 4}, HostRange{partial_out, sizeof(Packed)}, HostRange{workspace, pl.ws_bytes});
     switch (fam) {
         case FAM_SUM: return launch_partial<SumAcc>(pl, x, global_offset, out, workspace, st);
         case FAM_MOM: return launch_partial<MomAcc>(pl, x, global_offset, out, workspace, st);
@@ -739,6 +744,7 @@ extern "C" int tpb200_reduce_combine(int op, const void* partials, int n_parts, 
     cudaStream_t st = (cudaStream_t)stream;
     const Packed* p = (const Packed*)partials;
     const double cnt = (double)total_count;
+    TPB_CHECK_RANGES(st, HostRange{partials, (size_t)n_parts * sizeof(Packed)}, HostRange{ov, 4}, HostRange{oi, 8});
     switch (fam) {
         case FAM_SUM: return launch_combine<SumAcc>(p, n_parts, cnt, e, ov, oi, st);
         case FAM_MOM: return launch_combine<MomAcc>(p, n_parts, cnt, e, ov, oi, st);
@@ -821,6 +827,7 @@ extern "C" int tpb200_reduce_all_noalloc(int op, const void* in, int dtype, int6
     long long* oi = wants_idx ? (long long*)out_idx : nullptr;
     cudaStream_t st = (cudaStream_t)stream;
     const float* x = (const float*)in;
+    TPB_CHECK_RANGES(st, HostRange{in, (size_t)n * 4}, HostRange{ov, 4}, HostRange{oi, 8}, HostRange{scratch, pl.ws_bytes});
     switch (fam) {
         case FAM_SUM: return launch_plan<SumAcc>(pl, x, e, ov, oi, scratch, st);
         case FAM_MOM: return launch_plan<MomAcc>(pl, x, e, ov, oi, scratch, st);
@@ -890,7 +897,7 @@ finalize_exchange_kernel(const Packed* __restrict__ ws, int S, long long idx_off
     r.finish_thread();
     for (int q = lane; q < S; q += 32) {
         Acc o;
-        o.load(&ws[q]);
+        o.load(TPB_CK(&ws[q]));
         r.merge(o);
     }
     warp_combine(r);
@@ -900,24 +907,24 @@ finalize_exchange_kernel(const Packed* __restrict__ ws, int S, long long idx_off
         Packed rec;
         r.store(&rec);
         if (rec.i0 != kNoIndex) rec.i0 += idx_offset;
-        ep = mine->epoch + 1u;
+        ep = *TPB_CK(&mine->epoch) + 1u;
         const int par = (int)(ep & 1u);
-        for (int j = 0; j < world; ++j) peers.p[j]->slots[par][rank] = rec;     // peer-to-peer stores
+        for (int j = 0; j < world; ++j) *TPB_CK(&peers.p[j]->slots[par][rank]) = rec;     // peer-to-peer stores
         __threadfence_system();
-        for (int j = 0; j < world; ++j) st_release_sys(&peers.p[j]->flags[rank], ep);
+        for (int j = 0; j < world; ++j) st_release_sys(TPB_CK(&peers.p[j]->flags[rank]), ep);
         // bounded wait for every rank's record of this epoch
         for (int j = 0; j < world && ok; ++j) {
             int spin = 0;
-            while ((int)(ld_acquire_sys(&mine->flags[j]) - ep) < 0) {
+            while ((int)(ld_acquire_sys(TPB_CK(&mine->flags[j])) - ep) < 0) {
                 if (++spin > max_polls) { ok = false; break; }
                 __nanosleep(100);
             }
         }
-        mine->epoch = ep;
+        *TPB_CK(&mine->epoch) = ep;
         if (!ok) {
             if (status) atomicMax(status, kErrExchange);
-            if (ov) ov[0] = NAN;
-            if (oi) oi[0] = -1;
+            if (ov) *TPB_CK(&ov[0]) = NAN;
+            if (oi) *TPB_CK(&oi[0]) = -1;
         } else {
             // the same rank-ordered merge on every GPU
             Acc all;
@@ -925,7 +932,7 @@ finalize_exchange_kernel(const Packed* __restrict__ ws, int S, long long idx_off
             all.finish_thread();
             for (int j = 0; j < world; ++j) {
                 Acc o;
-                o.load(&mine->slots[par][j]);
+                o.load(TPB_CK(&mine->slots[par][j]));
                 all.merge(o);
             }
             write_result(all, e, total_count, ov, oi, 0);
@@ -978,6 +985,14 @@ extern "C" int tpb200_reduce_fused_exchange(int op, const void* in, int dtype, i
     int* status = device_status_word();
     const double tc = (double)total_count;
     const int max_polls = g_exchange_polls.load(std::memory_order_relaxed);
+#ifdef TPB200_CHECKED
+    {
+        HostRange rr[4 + kMaxPeers] = {HostRange{in, (size_t)n * 4}, HostRange{ov, 4}, HostRange{oi, 8}, HostRange{workspace, pl.ws_bytes}};
+        for (int j = 0; j < world; ++j) rr[4 + j] = HostRange{peer_buffers[j], sizeof(ExchangeBuf)};
+        const int crc = check_register(st, rr, 4 + world);
+        if (crc) return crc;
+    }
+#endif
 #define TPB_LAUNCH_X(ACC)                                                                                    \
     do {                                                                                                     \
         TPB_LAUNCH("row_split_kernel", row_split_kernel<ACC>, dim3((unsigned)pl.S), pl.threads, 0, st, x, pl.row, pl.chunk, pl.S, (Packed*)workspace); \

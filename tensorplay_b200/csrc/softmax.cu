@@ -18,6 +18,7 @@
 //                           (slices of up to 24 K elements; longer ones are read again, from L2 at best)
 //   any other dim of a contiguous tensor, viewed as [outer, C, inner]:
 //     softmax_col_kernel    a thread per (outer, inner) column, coalesced along inner, two sweeps
+#define TPB_FILE_ID 4
 #include "common.cuh"
 #include "host_util.h"
 
@@ -119,12 +120,12 @@ softmax_warp_kernel(const float* __restrict__ in, float* __restrict__ out, long 
         const float o2 = LOG ? (v[u].z - m) - log_s : fast_exp(v[u].z - m) * inv_s;
         const float o3 = LOG ? (v[u].w - m) - log_s : fast_exp(v[u].w - m) * inv_s;
         if (vec && e0 + 3 < len) {
-            *reinterpret_cast<float4*>(q + e0) = make_float4(o0, o1, o2, o3);
+            *reinterpret_cast<float4*>(TPB_CKN(q + e0, 16)) = make_float4(o0, o1, o2, o3);
         } else {
-            if (e0 < len) q[e0] = o0;
-            if (e0 + 1 < len) q[e0 + 1] = o1;
-            if (e0 + 2 < len) q[e0 + 2] = o2;
-            if (e0 + 3 < len) q[e0 + 3] = o3;
+            if (e0 < len) *TPB_CK(&q[e0]) = o0;
+            if (e0 + 1 < len) *TPB_CK(&q[e0 + 1]) = o1;
+            if (e0 + 2 < len) *TPB_CK(&q[e0 + 2]) = o2;
+            if (e0 + 3 < len) *TPB_CK(&q[e0 + 3]) = o3;
         }
     }
 }
@@ -181,7 +182,7 @@ softmax_long_kernel(const float* __restrict__ in, float* __restrict__ out, long 
             if (STAGE) reinterpret_cast<float4*>(stage)[i] = v;
             acc.add4(v.x, v.y, v.z, v.w);
         }
-        for (long long j = (nvec << 2) + tid; j < n; j += nthr) acc.add(p[j]);
+        for (long long j = (nvec << 2) + tid; j < n; j += nthr) acc.add(*TPB_CK(&p[j]));
     }
     // ---- the CTA's pair (every thread ends up with it), then the row's pair
     const int nw = nthr >> 5;
@@ -216,11 +217,11 @@ softmax_long_kernel(const float* __restrict__ in, float* __restrict__ out, long 
             o.y = LOG ? (v.y - m) - log_s : fast_exp(v.y - m) * inv_s;
             o.z = LOG ? (v.z - m) - log_s : fast_exp(v.z - m) * inv_s;
             o.w = LOG ? (v.w - m) - log_s : fast_exp(v.w - m) * inv_s;
-            *reinterpret_cast<float4*>(q + (i << 2)) = o;
+            *reinterpret_cast<float4*>(TPB_CKN(q + (i << 2), 16)) = o;
         }
         for (long long j = (nvec << 2) + tid; j < n; j += nthr) {
-            const float x = p[j];
-            q[j] = LOG ? (x - m) - log_s : fast_exp(x - m) * inv_s;
+            const float x = *TPB_CK(&p[j]);
+            *TPB_CK(&q[j]) = LOG ? (x - m) - log_s : fast_exp(x - m) * inv_s;
         }
     }
     // a CTA must not leave while the others may still write their pair into its shared memory:
@@ -242,14 +243,14 @@ softmax_col_kernel(const float* __restrict__ in, float* __restrict__ out, long l
     acc.init();
     long long j = 0;
     for (; j + 3 < C; j += 4) {
-        const float x0 = p[j * inner], x1 = p[(j + 1) * inner], x2 = p[(j + 2) * inner], x3 = p[(j + 3) * inner];
+        const float x0 = *TPB_CK(&p[j * inner]), x1 = *TPB_CK(&p[(j + 1) * inner]), x2 = *TPB_CK(&p[(j + 2) * inner]), x3 = *TPB_CK(&p[(j + 3) * inner]);
         acc.add4(x0, x1, x2, x3);
     }
-    for (; j < C; ++j) acc.add(p[j * inner]);
+    for (; j < C; ++j) acc.add(*TPB_CK(&p[j * inner]));
     const float m = acc.m, log_s = logf(acc.s), inv_s = 1.0f / acc.s;
     for (j = 0; j < C; ++j) {
-        const float x = p[j * inner];
-        q[j * inner] = LOG ? (x - m) - log_s : fast_exp(x - m) * inv_s;
+        const float x = *TPB_CK(&p[j * inner]);
+        *TPB_CK(&q[j * inner]) = LOG ? (x - m) - log_s : fast_exp(x - m) * inv_s;
     }
 }
 
@@ -273,6 +274,7 @@ extern "C" int tpb200_softmax(int log, const void* in, int dtype, int ndim, cons
     if (!in || !out) return fail(TPB200_ERR_INVALID, "NULL pointer argument");
     const long long C = sizes[d];
     cudaStream_t st = (cudaStream_t)stream;
+    TPB_CHECK_RANGES(st, view_range(in, ndim, sizes, strides, 4), HostRange{out, (size_t)numel * 4});
     const float* x = (const float*)in;
     float* y = (float*)out;
 

@@ -19,6 +19,7 @@
 // barrier while streaming) and topk_stream_kernel (k <= 2048: a buffer cut by the whole CTA at a
 // rendezvous).  Rows of at most 4096 elements are sorted whole in shared memory instead; rows
 // split over several CTAs are merged by a second, tiny kernel.
+#define TPB_FILE_ID 2
 #include "common.cuh"
 #include "host_util.h"
 
@@ -568,7 +569,7 @@ __device__ __forceinline__ void stream_body(const float* __restrict__ row, const
                 const int j = __ffs(m) - 1;
                 const long long e = elem_off(off, j);
                 if (e < len) {
-                    const float xv = slice[e * g.es];
+                    const float xv = *TPB_CK(&slice[e * g.es]);
                     const unsigned long long w = rank_word<LARGEST>(xv, (unsigned)(begin + e));
                     if (w > tau) {
                         const int pos = atomicAdd(&sh.cnt, 1);
@@ -623,7 +624,7 @@ __device__ __forceinline__ void stream_body(const float* __restrict__ row, const
     const int cnt = sh.cnt;
     if (ws) {
         unsigned long long* dst = ws + ((size_t)r * g.S + s) * (size_t)k;
-        for (int j = tid; j < k; j += kStreamThreads) dst[j] = j < cnt ? buf[j] : 0ull;
+        for (int j = tid; j < k; j += kStreamThreads) *TPB_CK(&dst[j]) = j < cnt ? buf[j] : 0ull;
     } else {
         for (int j = tid; j < k && j < cnt; j += kStreamThreads) {
             const unsigned long long w = buf[j];
@@ -631,9 +632,9 @@ __device__ __forceinline__ void stream_body(const float* __restrict__ row, const
             const unsigned key = (unsigned)(w >> 32);
             float val = key_value<LARGEST>(key);
             // the key folds -0.0 onto +0.0 and all NaNs onto one rank: those come from the row
-            if (key == 0u || val == 0.0f) val = row[(long long)idx * g.es];
-            out_idx[r * k + j] = (long long)idx;
-            out_val[r * k + j] = val;
+            if (key == 0u || val == 0.0f) val = *TPB_CK(&row[(long long)idx * g.es]);
+            *TPB_CK(&out_idx[r * k + j]) = (long long)idx;
+            *TPB_CK(&out_val[r * k + j]) = val;
         }
     }
 }
@@ -843,7 +844,7 @@ topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
                 m &= m - 1u;
                 const long long e = elem_off(off, j);
                 if (e < len) {
-                    const float xv = slice[e * g.es];
+                    const float xv = *TPB_CK(&slice[e * g.es]);
                     const unsigned long long w = rank_word<LARGEST>(xv, (unsigned)(begin + e));
                     if (w > tnow) {
                         const unsigned pos = atomicAdd(&sh.cnt, 1u);
@@ -967,15 +968,15 @@ topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     auto emit = [&](unsigned long long w, int rank) {
         if (w == 0ull || rank >= k) return;
         if (ws) {
-            ws[((size_t)r * g.S + s) * (size_t)k + rank] = w;
+            *TPB_CK(&ws[((size_t)r * g.S + s) * (size_t)k + rank]) = w;
         } else {
             const unsigned idx = word_index(w);
             const unsigned key = (unsigned)(w >> 32);
             float val = key_value<LARGEST>(key);
             // the key folds -0.0 onto +0.0 and all NaNs onto one rank: those come from the row
-            if (key == 0u || val == 0.0f) val = row[(long long)idx * g.es];
-            out_idx[r * k + rank] = (long long)idx;
-            out_val[r * k + rank] = val;
+            if (key == 0u || val == 0.0f) val = *TPB_CK(&row[(long long)idx * g.es]);
+            *TPB_CK(&out_idx[r * k + rank]) = (long long)idx;
+            *TPB_CK(&out_val[r * k + rank]) = val;
         }
     };
     if (!cut_chunk(ring, &sh, c_last, n_new, k, lane, status)) {
@@ -1003,7 +1004,7 @@ topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long l
             buf[i] = i < n_items ? rank_word<LARGEST>(ld_stream1(row + (long long)i * g.es), (unsigned)i) : 0ull;
     } else {
         const unsigned long long* src = ws + (size_t)r * n_items;
-        for (int i = tid; i < N; i += nthr) buf[i] = i < n_items ? src[i] : 0ull;
+        for (int i = tid; i < N; i += nthr) buf[i] = i < n_items ? *TPB_CK(&src[i]) : 0ull;
     }
     __syncthreads();
     bitonic_desc(buf, N, tid, nthr);
@@ -1013,8 +1014,8 @@ topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long l
         // a slice kernel that gave up (status word set) leaves its words unwritten: never follow
         // an index that is not inside the row
         const bool inside = (long long)idx < g.len;
-        out_idx[r * k + j] = inside ? (long long)idx : -1LL;
-        out_val[r * k + j] = inside ? row[(long long)idx * g.es] : NAN;
+        *TPB_CK(&out_idx[r * k + j]) = inside ? (long long)idx : -1LL;
+        *TPB_CK(&out_val[r * k + j]) = inside ? *TPB_CK(&row[(long long)idx * g.es]) : NAN;
     }
 }
 
@@ -1032,8 +1033,8 @@ topk_merge_pairs_kernel(const float* __restrict__ cv, const long long* __restric
     const int tid = threadIdx.x, nthr = blockDim.x;
     for (int i = tid; i < N; i += nthr) {
         if (i < n) {
-            skey[i] = rank_key<LARGEST>(cv[i]);
-            sidx[i] = ci[i] + (list_off ? list_off[i / list_len] : 0LL);
+            skey[i] = rank_key<LARGEST>(*TPB_CK(&cv[i]));
+            sidx[i] = *TPB_CK(&ci[i]) + (list_off ? *TPB_CK(&list_off[i / list_len]) : 0LL);
             sslot[i] = i;
         }
         else { skey[i] = 0u; sidx[i] = kNoIndex; sslot[i] = -1; }
@@ -1061,8 +1062,8 @@ topk_merge_pairs_kernel(const float* __restrict__ cv, const long long* __restric
         }
     }
     for (int j = tid; j < k; j += nthr) {
-        out_idx[j] = sidx[j];
-        out_val[j] = cv[sslot[j]];
+        *TPB_CK(&out_idx[j]) = sidx[j];
+        *TPB_CK(&out_val[j]) = *TPB_CK(&cv[sslot[j]]);
     }
 }
 
@@ -1070,7 +1071,11 @@ __device__ __forceinline__ int pow2_ceil_dev(int v) { return v <= 1 ? 1 : 1 << (
 
 }  // namespace tpb
 
+#undef TPB_FILE_ID
+#define TPB_FILE_ID 3
 #include "topk_select.cuh"
+#undef TPB_FILE_ID
+#define TPB_FILE_ID 2
 
 namespace tpb {
 
@@ -1458,6 +1463,8 @@ extern "C" int tpb200_topk(const void* in, int dtype, int ndim, const int64_t* s
         if (((uintptr_t)workspace) & 7) return fail(TPB200_ERR_WORKSPACE, "workspace must be 8-byte aligned");
     }
     cudaStream_t st = (cudaStream_t)stream;
+    TPB_CHECK_RANGES(st, view_range(in, ndim, sizes, strides, 4), HostRange{out_val, (size_t)pl.out_numel * 4},
+                     HostRange{out_idx, (size_t)pl.out_numel * 8}, HostRange{workspace, pl.ws_bytes});
     if (largest) return topk_launch<true>(pl, (const float*)in, (float*)out_val, (long long*)out_idx, workspace, st);
     return topk_launch<false>(pl, (const float*)in, (float*)out_val, (long long*)out_idx, workspace, st);
 }
@@ -1478,6 +1485,9 @@ extern "C" int tpb200_topk_merge(const float* cand_val, const int64_t* cand_idx,
     const size_t sm = (size_t)N * (8 + 4 + 4);
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = std::min(kSortThreads, std::max(32, N / 2));
+    TPB_CHECK_RANGES(st, HostRange{cand_val, (size_t)n_cand * 4}, HostRange{cand_idx, (size_t)n_cand * 8},
+                     HostRange{list_offsets, list_offsets ? (size_t)(n_cand / ll) * 8 : 0},
+                     HostRange{out_val, (size_t)k * 4}, HostRange{out_idx, (size_t)k * 8});
     if (largest) {
         int rc = allow_smem(topk_merge_pairs_kernel<true>, sm);
         if (rc) return rc;

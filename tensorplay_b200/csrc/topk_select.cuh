@@ -113,9 +113,9 @@ __device__ bool sel_final(unsigned long long* cand, int n, int k, int cap, unsig
     auto emit = [&](int j, unsigned long long w) {
         const unsigned idx = word_index(w);
         float val = key_value<LARGEST>((unsigned)(w >> 32));
-        if (val == 0.0f) val = row[(long long)idx * es];   // the key folds -0.0 onto +0.0: the sign comes from the row
-        oi[j] = (long long)idx;
-        ov[j] = val;
+        if (val == 0.0f) val = *TPB_CK(&row[(long long)idx * es]);   // the key folds -0.0 onto +0.0: the sign comes from the row
+        *TPB_CK(&oi[j]) = (long long)idx;
+        *TPB_CK(&ov[j]) = val;
     };
     if (tid == 0) sh.tmp = 0;
     __syncthreads();
@@ -403,7 +403,7 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
             m &= m - 1u;
             const long long e = elem_off(off, j);
             if (e < len) {
-                const float xv = slice[e * g.es];
+                const float xv = *TPB_CK(&slice[e * g.es]);
                 const int pos = atomicAdd(&sh.cnt, 1);
                 if (pos < cap) cand[pos] = rank_word<LARGEST>(xv, (unsigned)(begin + e));
             }

@@ -26,3 +26,18 @@ def cuda():
 
     _lib.lib()  # fail loudly if the extension is missing
     return torch.device("cuda", 0)
+
+
+@pytest.fixture(autouse=True)
+def _no_range_violation(request):
+    """Under TPB200_CHECKED=1 (the range-checking build of the library) every GPU test also asserts that
+    no kernel touched memory outside the ranges its entry point registered."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    from tensorplay_b200 import _lib
+
+    if not _lib.CHECKED or _lib._lib is None:
+        return
+    rep = _lib.check_report()
+    assert rep["violations"] == 0, f"range violations under the checked build: {rep}"
