@@ -317,6 +317,71 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
     return cases
 
 
+# Small single-kernel cases for profiler captures: the same kernels as the suite on inputs of a few
+# hundred MB (larger than L2, so DRAM counters mean something; small enough for a many-pass capture).
+PROFILE_CASES = ("topk_c2", "topk_64x1048576_k1024", "sum_c1", "softmax_c1", "softmax_c2", "median_c1",
+                 "sum02_16x4096x512", "std02_16x4096x512", "prod02_16x4096x512", "permute_copy_16x4096x512",
+                 "sum_2p28")
+
+
+def build_profile_case(torch, tpb, dev, name: str):
+    gen = torch.Generator(device=dev).manual_seed(4321)
+    if name in ("topk_c2", "softmax_c2"):
+        xs = [gen_c2(torch, dev, gen) for _ in range(2)]
+        inb = 256 * 151936 * 4
+        if name == "topk_c2":
+            ov = torch.empty(256, 50, device=dev)
+            oi = torch.empty(256, 50, dtype=torch.int64, device=dev)
+            return Case("topk k=50 [256,151936]", lambda i: tpb.topk(xs[i % 2], 50, -1, True, True, out=(ov, oi)), inb + 256 * 50 * 12, 256, 1, xs)
+        o = torch.empty(256, 151936, device=dev)
+        return Case("softmax dim=-1 [256,151936]", lambda i: tpb.softmax(xs[i % 2], -1, out=o), 2 * inb, 256, 1, xs)
+    if name == "topk_64x1048576_k1024":
+        xs = [gen_c5(torch, dev, gen, 64) for _ in range(2)]
+        ov = torch.empty(64, 1024, device=dev)
+        oi = torch.empty(64, 1024, dtype=torch.int64, device=dev)
+        return Case("topk k=1024 [64,1048576]", lambda i: tpb.topk(xs[i % 2], 1024, -1, True, True, out=(ov, oi)), 64 * ((1 << 20) * 4 + 1024 * 12), 64, 1, xs)
+    if name in ("sum_c1", "softmax_c1", "median_c1"):
+        xs = [gen_c1(torch, dev, gen) for _ in range(4)]
+        inb = 4096 * 4096 * 4
+        if name == "sum_c1":
+            ov = torch.empty(4096, device=dev)
+            return Case("sum dim=-1 [4096,4096]", lambda i: tpb.sum(xs[i % 4], -1, out=ov), inb + 16384, 4096, 1, xs)
+        if name == "median_c1":
+            om = torch.empty((), device=dev)
+            return Case("median [4096,4096]", lambda i: tpb.median(xs[i % 4], out=om), inb + 4, 1, 7, xs)
+        o = torch.empty(4096, 4096, device=dev)
+        return Case("softmax dim=-1 [4096,4096]", lambda i: tpb.softmax(xs[i % 4], -1, out=o), 2 * inb, 4096, 1, xs)
+    if name.endswith("16x4096x512"):
+        xs = [gen_c3(torch, dev, gen, 16) for _ in range(2)]
+        inb = 16 * 4096 * 512 * 4
+        if name.startswith("permute_copy"):
+            perm = torch.empty(16, 512, 4096, device=dev)
+            return Case("permute(0,2,1) copy [16,4096,512]", lambda i: tpb.copy_(perm, xs[i % 2].permute(0, 2, 1)), 2 * inb, 16 * 512, 1, xs)
+        ov = torch.empty(4096, device=dev)
+        fn = {"sum02": tpb.sum, "std02": tpb.std, "prod02": tpb.prod}[name.split("_")[0]]
+        return Case(f"{name.split('_')[0][:-2]} dims=(0,2) [16,4096,512]", lambda i: fn(xs[i % 2], [0, 2], out=ov), inb + 16384, 4096, 1, xs)
+    if name == "sum_2p28":
+        x = gen_c4(torch, dev, gen, 1 << 28)
+        return Case("sum whole tensor 2^28", lambda i: tpb.sum(x), (1 << 30) + 4, 1, 2, [x])
+    raise ValueError(name)
+
+
+def run_profile_case(args):
+    """`--profile-case NAME`: warm-up plus --steps eager launches of one small case, one JSON line.  This is
+    the command a profiler wraps; the line it prints under a profiler is not a benchmark value."""
+    import torch
+    import tensorplay_b200 as tpb
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    case = build_profile_case(torch, tpb, dev, args.profile_case)
+    ms, _ = device_time_ms(torch, case, args.steps, args.warmup, use_graph=False)
+    peak, _ = measured_peak()
+    gbs = case.alg_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({"profile_case": args.profile_case, "case": case.name, "us": round(ms * 1e3, 2), "GB/s": round(gbs, 1),
+                      "pct_of_measured_peak": round(100 * gbs / peak, 1), "algorithmic_bytes_per_launch": case.alg_bytes,
+                      "launches_per_step": case.launches, "timing": "eager launches, CUDA events"}))
+
+
 def e2e_c2(torch, tpb, dev, steps: int, warmup: int):
     """Top-k through the public call with the batch in pinned host memory: every step copies the
     batch host->device, runs the kernels and copies values + indices back."""
@@ -568,9 +633,14 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--no-suite", action="store_true", help="skip the other configurations")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph")
+    ap.add_argument("--profile-case", default=None, choices=PROFILE_CASES,
+                    help="run one small single-kernel case eagerly (the command a profiler wraps) and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.profile_case:
+        run_profile_case(args)
         return
 
     import torch

@@ -21,6 +21,14 @@
 //                                    with the partition offsets applied in the kernel.
 #include "host_util.h"
 
+// A checked build keeps one range table per device: where several logical GPUs of a comm share a device,
+// their calls must not overlap, so each one is waited for.  (The fused mode needs distinct devices.)
+#ifdef TPB200_CHECKED
+#define TPB_CHECKED_SERIALIZE(st) TPB_CUDA_OK(cudaStreamSynchronize(st))
+#else
+#define TPB_CHECKED_SERIALIZE(st) do { } while (0)
+#endif
+
 #include <algorithm>
 #include <new>
 #include <vector>
@@ -234,6 +242,7 @@ extern "C" int tpb200_reduce_sharded(tpb200_comm* c, int op, const void* const* 
         rc = tpb200_reduce_partial(fam, parts[g], dtype, counts[g], offset[g], q.records + (size_t)g * TPB200_PARTIAL_BYTES,
                                    q.scratch, kCommScratchBytes, q.stream);
         if (rc) return rc;
+        TPB_CHECKED_SERIALIZE(q.stream);
         TPB_CUDA_OK(cudaEventRecord(q.ready, q.stream));
     }
     for (int d = 0; d < n; ++d) {
@@ -251,6 +260,7 @@ extern "C" int tpb200_reduce_sharded(tpb200_comm* c, int op, const void* const* 
         int64_t* oi = wants_idx ? (out_idx && out_idx[g] ? out_idx[g] : q.out_idx) : nullptr;
         rc = tpb200_reduce_combine(op, q.records, n, total, correction, ov, oi, q.stream);
         if (rc) return rc;
+        TPB_CHECKED_SERIALIZE(q.stream);
         // the next call overwrites the gather buffers of the others: they wait for this merge
         TPB_CUDA_OK(cudaEventRecord(q.gathered, q.stream));
     }
@@ -288,6 +298,7 @@ extern "C" int tpb200_topk_sharded(tpb200_comm* c, const void* const* parts, con
         int rc = tpb200_topk(parts[g], dtype, 1, sizes, strides, 0, k, largest, 1, q.cand_val + (size_t)g * k,
                              q.cand_idx + (size_t)g * k, q.scratch, kCommScratchBytes, q.stream);
         if (rc) return rc;
+        TPB_CHECKED_SERIALIZE(q.stream);
         TPB_CUDA_OK(cudaMemcpyAsync(q.offsets, offset.data(), sizeof(int64_t) * n, cudaMemcpyHostToDevice, q.stream));
         TPB_CUDA_OK(cudaEventRecord(q.ready, q.stream));
     }
@@ -306,6 +317,7 @@ extern "C" int tpb200_topk_sharded(tpb200_comm* c, const void* const* parts, con
         int64_t* oi = out_idx && out_idx[g] ? out_idx[g] : q.out_idx;
         int rc = tpb200_topk_merge(q.cand_val, q.cand_idx, (int64_t)n * k, k, largest, q.offsets, k, ov, oi, q.stream);
         if (rc) return rc;
+        TPB_CHECKED_SERIALIZE(q.stream);
         TPB_CUDA_OK(cudaEventRecord(q.gathered, q.stream));
     }
     for (int g = 0; g < n; ++g) {
