@@ -45,10 +45,12 @@ NOMINAL_PEAK_GBS = 8000.0
 # DRAM traffic per launch of the dominant kernel from one ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum).  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    "c2": None,                      # topk_select_kernel: filled in from the capture of this kernel
+    "c2": 155_654_912 + 4_059_392,   # topk_smallk_kernel, [256,151936] k = 50 (algorithmic 155.74 MB)
     "c1": 67_143_424 + 418_816,      # row_warp_kernel
     "c3": 536_887_808 + 6_670_848,   # col_kernel
-    "c5": None,
+    # topk_select_kernel captured on [64, 2^20] k = 1024 (269.80 MB read + 3.39 MB written for an
+    # algorithmic 269.22 MB) and scaled by 8 to the 512 rows of a launch: traffic is per row
+    "c5": 8 * (269_800_960 + 3_386_880),
 }
 
 
@@ -707,7 +709,7 @@ def main():
     line["roofline"] = {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                         "frac": round(per_gpu / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
-                        "kernel": {"c2": "topk_select_kernel", "c5": "topk_select_kernel"}.get(args.workload, case.name),
+                        "kernel": {"c2": "topk_smallk_kernel", "c5": "topk_select_kernel"}.get(args.workload, case.name),
                         "algorithmic_bytes_per_launch": case.alg_bytes}
 
     # end to end (host buffers) for the headline

@@ -11,6 +11,7 @@
 //
 //   dim is the last, contiguous dim ("rows"):
 //     softmax_warp_kernel   one warp per row, the row in registers            (rows of up to 1024)
+//     softmax_reg_kernel    one CTA per 16-byte aligned row of 1025 .. 16384 elements, the row in registers
 //     softmax_long_kernel   S CTAs per row (a cluster when S > 1): every thread keeps a running
 //                           (max, sum) pair over its part, the CTA's pair goes to every CTA of the
 //                           row through distributed shared memory, one cluster barrier, and the second
@@ -126,6 +127,66 @@ softmax_warp_kernel(const float* __restrict__ in, float* __restrict__ out, long 
             if (e0 + 1 < len) *TPB_CK(&q[e0 + 1]) = o1;
             if (e0 + 2 < len) *TPB_CK(&q[e0 + 2]) = o2;
             if (e0 + 3 < len) *TPB_CK(&q[e0 + 3]) = o3;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- one CTA per row, row in registers
+// Rows of 1025 .. 16384 elements (16-byte aligned, length a multiple of 4): every thread keeps its
+// VPT float4 in registers, so the row is read once and the exponentials are computed once.  With
+// the whole row at hand the plain chain of the reference is the cheapest form: the maximum (NaN
+// skipped, as in the reference's strict compare), e = exp(x - max), the sum, e / sum -- about seven
+// instructions per element where the running (max, sum) form with its rescaling and special cases
+// needed forty ([4096,4096]: 76 % of the issue slots busy at 27 us).  NaN, +inf and all -inf rows
+// come out as NaN through the arithmetic itself: exp(NaN), inf - inf.
+template <bool LOG, int VPT>
+__global__ void __launch_bounds__(512)
+softmax_reg_kernel(const float* __restrict__ in, float* __restrict__ out, long long k1, long long ks0,
+                   long long ks1, int len) {
+    __shared__ float red_m[16];
+    __shared__ float red_s[16];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x, nw = nthr >> 5;
+    const long long r = blockIdx.x;
+    const long long a = r / k1, b = r - a * k1;
+    const float* p = in + a * ks0 + b * ks1;
+    float* q = out + r * (long long)len;
+    const int nvec = len >> 2;
+    float4 v[VPT];
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int i = u * nthr + tid;
+        v[u] = i < nvec ? ld_stream4(p + 4 * i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) m = fmaxf(m, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+    m = warp_max(m);
+    if (lane == 0) red_m[warp] = m;
+    __syncthreads();
+    m = warp_max(lane < nw ? red_m[lane] : -INFINITY);
+    // padding is -inf: exp(-inf - m) = 0 for every m but -inf, and a row of nothing but -inf is NaN anyway
+    float s = 0.0f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const float e0 = fast_exp(v[u].x - m), e1 = fast_exp(v[u].y - m), e2 = fast_exp(v[u].z - m), e3 = fast_exp(v[u].w - m);
+        s += (e0 + e1) + (e2 + e3);
+        if (!LOG) v[u] = make_float4(e0, e1, e2, e3);
+    }
+    s = (float)warp_sum((double)s);
+    if (lane == 0) red_s[warp] = s;
+    __syncthreads();
+    s = (float)warp_sum(lane < nw ? (double)red_s[lane] : 0.0);
+    const float log_s = logf(s), inv_s = 1.0f / s;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int i = u * nthr + tid;
+        if (i < nvec) {
+            float4 o;
+            o.x = LOG ? (v[u].x - m) - log_s : v[u].x * inv_s;
+            o.y = LOG ? (v[u].y - m) - log_s : v[u].y * inv_s;
+            o.z = LOG ? (v[u].z - m) - log_s : v[u].z * inv_s;
+            o.w = LOG ? (v[u].w - m) - log_s : v[u].w * inv_s;
+            *reinterpret_cast<float4*>(TPB_CKN(q + 4 * i, 16)) = o;
         }
     }
 }
@@ -320,6 +381,19 @@ extern "C" int tpb200_softmax(int log, const void* in, int dtype, int ndim, cons
     } while (0)
             if (C <= 128) TPB_SM_WARP(1); else if (C <= 256) TPB_SM_WARP(2); else if (C <= 512) TPB_SM_WARP(4); else TPB_SM_WARP(8);
 #undef TPB_SM_WARP
+            return TPB200_OK;
+        }
+        if (vec && C <= 16384) {
+            // threads so that a thread holds at most four float4 (eight above 8192 elements)
+            int threads = 128;
+            while (threads < 512 && (long long)threads * 16 < C) threads *= 2;
+            if (rows > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
+            const dim3 grid((unsigned)rows);
+            const bool v8 = (long long)threads * 16 < C;
+#define TPB_SM_REG(LOGV, V) TPB_LAUNCH("softmax_reg_kernel", (softmax_reg_kernel<LOGV, V>), grid, threads, 0, st, x, y, k1, ks0, ks1, (int)C)
+            if (log) { if (v8) TPB_SM_REG(true, 8); else TPB_SM_REG(true, 4); }
+            else     { if (v8) TPB_SM_REG(false, 8); else TPB_SM_REG(false, 4); }
+#undef TPB_SM_REG
             return TPB200_OK;
         }
         // Rows of up to 48 K elements: one or two CTAs per row, each keeping its slice (at most 24 K
