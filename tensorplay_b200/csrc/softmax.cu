@@ -54,6 +54,27 @@ struct MaxSum {
         }
         s += (fast_exp(a - m) + fast_exp(b - m)) + (fast_exp(c - m) + fast_exp(d - m));
     }
+    // sixteen values at once (the streaming loops of the long rows): one compare against the running
+    // maximum and one test for the all -inf start per sixteen elements -- the kernel was bound by
+    // instruction issue, not by memory, while it did both per four
+    __device__ __forceinline__ void add16(const float4 (&v)[4]) {
+        float cm = fmaxf(fmaxf(v[0].x, v[0].y), fmaxf(v[0].z, v[0].w));
+#pragma unroll
+        for (int u = 1; u < 4; ++u) cm = fmaxf(cm, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+        if (cm > m) { s *= fast_exp(m - cm); m = cm; }
+        if (m == -INFINITY) {
+            float t = 0.0f;   // -inf and NaN only: the sum is NaN iff one of them is NaN
+#pragma unroll
+            for (int u = 0; u < 4; ++u) t += (v[u].x + v[u].y) + (v[u].z + v[u].w);
+            if (t != t) s = NAN;
+            return;
+        }
+        float t = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            t += (fast_exp(v[u].x - m) + fast_exp(v[u].y - m)) + (fast_exp(v[u].z - m) + fast_exp(v[u].w - m));
+        s += t;
+    }
     __device__ __forceinline__ void add(float a) {
         if (a > m) { s *= fast_exp(m - a); m = a; }
         if (m == -INFINITY) { if (a != a) s = NAN; return; }
@@ -232,11 +253,11 @@ softmax_long_kernel(const float* __restrict__ in, float* __restrict__ out, long 
             float4 v[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) v[u] = STAGE ? ld_stream4(p + ((i + (long long)u * nthr) << 2)) : ld_keep4(p + ((i + (long long)u * nthr) << 2));
+            if (STAGE) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (STAGE) reinterpret_cast<float4*>(stage)[i + (long long)u * nthr] = v[u];
-                acc.add4(v[u].x, v[u].y, v[u].z, v[u].w);
+                for (int u = 0; u < 4; ++u) reinterpret_cast<float4*>(stage)[i + (long long)u * nthr] = v[u];
             }
+            acc.add16(v);
         }
         for (; i < nvec; i += nthr) {
             const float4 v = STAGE ? ld_stream4(p + (i << 2)) : ld_keep4(p + (i << 2));
@@ -271,6 +292,22 @@ softmax_long_kernel(const float* __restrict__ in, float* __restrict__ out, long 
     // ---- sweep 2: the slice again (L2), result out
     {
         long long i = tid;
+        // four loads in flight per thread here too: the slice comes from L2 at best
+        for (; i + 3LL * nthr < nvec; i += 4LL * nthr) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                v[u] = STAGE ? reinterpret_cast<const float4*>(stage)[i + (long long)u * nthr] : ld_stream4(p + ((i + (long long)u * nthr) << 2));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                float4 o;
+                o.x = LOG ? (v[u].x - m) - log_s : fast_exp(v[u].x - m) * inv_s;
+                o.y = LOG ? (v[u].y - m) - log_s : fast_exp(v[u].y - m) * inv_s;
+                o.z = LOG ? (v[u].z - m) - log_s : fast_exp(v[u].z - m) * inv_s;
+                o.w = LOG ? (v[u].w - m) - log_s : fast_exp(v[u].w - m) * inv_s;
+                *reinterpret_cast<float4*>(TPB_CKN(q + ((i + (long long)u * nthr) << 2), 16)) = o;
+            }
+        }
         for (; i < nvec; i += nthr) {
             const float4 v = STAGE ? reinterpret_cast<const float4*>(stage)[i] : ld_stream4(p + (i << 2));
             float4 o;
@@ -399,9 +436,11 @@ extern "C" int tpb200_softmax(int log, const void* in, int dtype, int ndim, cons
         // Rows of up to 48 K elements: one or two CTAs per row, each keeping its slice (at most 24 K
         // elements, 96 KB: two CTAs per SM) in shared memory between the sweeps, so the input is read
         // once.  Longer rows: the second sweep reads the slice again, and S only has to give the GPU
-        // enough CTAs (two per SM).  Measured on [256,151936] (algorithmic 311 MB): S = 8 with staged
-        // slices 84 us -- seven waves of CTAs that each load, wait for their cluster and only then
-        // store; S = 1 / 2 / 4 without staging 80 / 74 / 77 us.
+        // enough CTAs (two per SM).  Measured on [256,151936] (algorithmic 311 MB, four inputs in
+        // rotation): S = 8 with staged slices 84 us -- seven waves of CTAs that each load, wait for
+        // their cluster and only then store; S = 1 / 2 / 4 without staging 79 / 72 / 76 us.  72 us is
+        // what two reads and one write of the tensor (467 MB) take at the copy bandwidth: with 512 CTAs
+        // sweeping 304 KB each the second sweep finds little of its slice left in L2.
         constexpr long long kStageMax = 24 * 1024;
         int S = 1;
         if (C > kStageMax && C <= 2 * kStageMax) S = 2;
