@@ -12,7 +12,9 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 # TPB200_CHECKED=1 in the environment selects the range-checking build of the same sources
 # (libtpb200_checked.so: see "checked build" in include/tpb200.h); it must exist, nothing falls back.
 CHECKED = os.environ.get("TPB200_CHECKED", "") not in ("", "0")
-LIB_PATH = os.path.join(_PKG, "libtpb200_checked.so" if CHECKED else "libtpb200.so")
+# TPB200_TRACE=1 selects the development build with phase stamps (tensorplay_b200/trace.py reads them)
+TRACE = not CHECKED and os.environ.get("TPB200_TRACE", "") not in ("", "0")
+LIB_PATH = os.path.join(_PKG, "libtpb200_checked.so" if CHECKED else ("libtpb200_trace.so" if TRACE else "libtpb200.so"))
 
 # error codes of include/tpb200.h
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_DIM_RANGE, ERR_EMPTY, ERR_WORKSPACE, ERR_CUDA = range(7)
@@ -54,7 +56,7 @@ def lib() -> ctypes.CDLL:
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m tensorplay_b200.build{' --checked' if CHECKED else ''}` "
+            f"{LIB_PATH} is missing: build it with `python -m tensorplay_b200.build{' --checked' if CHECKED else (' --trace' if TRACE else '')}` "
             "(needs nvcc; there is no CPU or PyTorch fallback)")
     L = ctypes.CDLL(LIB_PATH)
     vp, i, i64, u64, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64, ctypes.c_size_t

@@ -17,6 +17,9 @@ LIB_PATH = os.path.join(_PKG, "libtpb200.so")
 # The same sources with -DTPB200_CHECKED: every global access range-checked (see include/tpb200.h).
 # Relocatable device code, because the range table and the violation record are shared by all files.
 LIB_PATH_CHECKED = os.path.join(_PKG, "libtpb200_checked.so")
+# The same sources with -DTPB200_TRACE: phase stamps (%globaltimer) in the sampled-threshold top-k kernel
+# and in the whole-tensor exchange, read by tensorplay_b200/trace.py.  A development build.
+LIB_PATH_TRACE = os.path.join(_PKG, "libtpb200_trace.so")
 
 SOURCES = ["api_common.cu", "reduce.cu", "topk.cu", "softmax.cu", "median.cu", "comm.cu", "copy.cu"]
 NVCC_FLAGS = [
@@ -42,17 +45,17 @@ def _stale(lib: str = LIB_PATH) -> bool:
     return any(os.path.getmtime(d) > t for d in deps if os.path.isfile(d))
 
 
-def build_library(force: bool = False, verbose: bool = False, checked: bool = False) -> str:
-    """Build libtpb200.so (or, with checked=True, libtpb200_checked.so) if it is missing or older than
-    its sources; returns its path."""
-    lib = LIB_PATH_CHECKED if checked else LIB_PATH
+def build_library(force: bool = False, verbose: bool = False, checked: bool = False, trace: bool = False) -> str:
+    """Build libtpb200.so (or, with checked=True, libtpb200_checked.so; with trace=True,
+    libtpb200_trace.so) if it is missing or older than its sources; returns its path."""
+    lib = LIB_PATH_CHECKED if checked else (LIB_PATH_TRACE if trace else LIB_PATH)
     if not force and not _stale(lib):
         return lib
     nvcc = _nvcc()
     # separately compiled device functions do not see their callers' launch bounds: one register cap for all
     # (40: the tightest launch bound in the sources, 512 threads x 3 CTAs per SM)
-    extra = ["-DTPB200_CHECKED", "-rdc=true", "-maxrregcount=40"] if checked else []
-    objdir = os.path.join(_PKG, "build_checked" if checked else "build")
+    extra = ["-DTPB200_CHECKED", "-rdc=true", "-maxrregcount=40"] if checked else (["-DTPB200_TRACE"] if trace else [])
+    objdir = os.path.join(_PKG, "build_checked" if checked else ("build_trace" if trace else "build"))
     os.makedirs(objdir, exist_ok=True)
     srcs = [s for s in SOURCES if os.path.exists(os.path.join(_CSRC, s))]
 
@@ -80,4 +83,5 @@ def build_library(force: bool = False, verbose: bool = False, checked: bool = Fa
 if __name__ == "__main__":
     import sys
 
-    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--checked" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--checked" in sys.argv,
+                        trace="--trace" in sys.argv))

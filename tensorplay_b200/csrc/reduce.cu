@@ -32,6 +32,22 @@
 
 namespace tpb {
 
+// Development builds (-DTPB200_TRACE) stamp the whole-tensor path with %globaltimer: slot 0 earliest
+// start and slot 1 latest end of the slice kernel's CTAs, slots 2..6 of the exchange kernel: start,
+// own partials merged, record and flag published to every rank, every rank's flag seen, result
+// written.  tpb200_debug_reduce_trace() reads them back.  Ordinary builds compile none of it.
+#ifdef TPB200_TRACE
+__device__ unsigned long long g_red_trace[8];
+__device__ __forceinline__ unsigned long long red_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TPB_RED_STAMP(i) (g_red_trace[i] = red_now())
+#define TPB_RED_STAMP_MIN(i) atomicMin(&g_red_trace[i], red_now())
+#define TPB_RED_STAMP_MAX(i) atomicMax(&g_red_trace[i], red_now())
+#else
+#define TPB_RED_STAMP(i) do { } while (0)
+#define TPB_RED_STAMP_MIN(i) do { } while (0)
+#define TPB_RED_STAMP_MAX(i) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------ geometry ---------------
 struct RowGeom {
     long long rows;                      // number of outputs
@@ -140,6 +156,7 @@ row_split_kernel(const float* __restrict__ in, RowGeom g, long long sub, int S, 
     __shared__ Acc sm[32];
     const int tid = threadIdx.x, nthr = blockDim.x;
     const long long s = blockIdx.x % (unsigned)S, r = blockIdx.x / (unsigned)S;
+    if (tid == 0) TPB_RED_STAMP_MIN(0);
     const float* p = row_base(in, g, r);
     Acc acc;
     acc.init();
@@ -149,7 +166,38 @@ row_split_kernel(const float* __restrict__ in, RowGeom g, long long sub, int S, 
     }
     acc.finish_thread();
     block_combine(acc, sm);
-    if (tid == 0) acc.store(TPB_CK(&ws[r * S + s]));
+    if (tid == 0) {
+        acc.store(TPB_CK(&ws[r * S + s]));
+        TPB_RED_STAMP_MAX(1);
+    }
+}
+
+// Lane `lane` of a warp merges partials lane, lane + 32, ... of `ws` into r, in that order.  Up to 640
+// partials (20 per lane) are loaded first and merged afterwards: with the load inside the merge loop
+// every step waited for its own load (the variance's merge is too long for the compiler to unroll the
+// loop: 8-9 us for 444 partials, against 1.4-2 us for the sum's 592).
+template <class Acc>
+__device__ __forceinline__ void merge_partials(Acc& r, const Packed* __restrict__ ws, int S, int lane) {
+    constexpr int kPre = 20;
+    if (S <= 32 * kPre) {
+        Acc part[kPre];
+#pragma unroll
+        for (int u = 0; u < kPre; ++u) {
+            const int q = lane + 32 * u;
+            if (q < S) part[u].load(TPB_CK(&ws[q]));
+        }
+#pragma unroll
+        for (int u = 0; u < kPre; ++u) {
+            const int q = lane + 32 * u;
+            if (q < S) r.merge(part[u]);
+        }
+    } else {
+        for (int q = lane; q < S; q += 32) {
+            Acc o;
+            o.load(TPB_CK(&ws[q]));
+            r.merge(o);
+        }
+    }
 }
 
 // Pass 2: one warp per row merges that row's S partials in a fixed order (lane l takes
@@ -165,11 +213,7 @@ finalize_kernel(const Packed* __restrict__ ws, long long rows, int S, double cou
     Acc acc;
     acc.init();
     acc.finish_thread();
-    for (int s = lane; s < S; s += 32) {
-        Acc o;
-        o.load(TPB_CK(&ws[r * S + s]));
-        acc.merge(o);
-    }
+    merge_partials(acc, ws + r * S, S, lane);
     warp_combine(acc);
     if (lane == 0) {
         if (packed_out) {
@@ -891,56 +935,82 @@ finalize_exchange_kernel(const Packed* __restrict__ ws, int S, long long idx_off
                          PeerPtrs peers, double total_count, Epilogue e, float* ov, long long* oi, int* status,
                          int max_polls) {
     const int lane = threadIdx.x & 31;
+    if (lane == 0) TPB_RED_STAMP(2);
     ExchangeBuf* mine = peers.p[rank];
     Acc r;
     r.init();
     r.finish_thread();
-    for (int q = lane; q < S; q += 32) {
-        Acc o;
-        o.load(TPB_CK(&ws[q]));
-        r.merge(o);
-    }
+    merge_partials(r, ws, S, lane);
     warp_combine(r);
-    bool ok = true;
-    unsigned ep = 0;
+    // Lane j talks to rank j: it stores this rank's record into rank j's buffer and then the flag with
+    // release semantics (which orders that lane's record stores before the flag, all the way to the
+    // peer), waits for rank j's flag and takes rank j's record.  All ranks are served at once: one lane
+    // doing the eight stores, a system-wide fence and eight release stores in turn took 13-17 us of an
+    // 8-GPU step; the flags and records of the peers cross NVLink in parallel this way.
+    __shared__ Packed rec_sh;
     if (lane == 0) {
-        Packed rec;
-        r.store(&rec);
-        if (rec.i0 != kNoIndex) rec.i0 += idx_offset;
-        ep = *TPB_CK(&mine->epoch) + 1u;
-        const int par = (int)(ep & 1u);
-        for (int j = 0; j < world; ++j) *TPB_CK(&peers.p[j]->slots[par][rank]) = rec;     // peer-to-peer stores
-        __threadfence_system();
-        for (int j = 0; j < world; ++j) st_release_sys(TPB_CK(&peers.p[j]->flags[rank]), ep);
-        // bounded wait for every rank's record of this epoch
-        for (int j = 0; j < world && ok; ++j) {
-            int spin = 0;
-            while ((int)(ld_acquire_sys(TPB_CK(&mine->flags[j])) - ep) < 0) {
-                if (++spin > max_polls) { ok = false; break; }
-                __nanosleep(100);
-            }
+        TPB_RED_STAMP(3);
+        r.store(&rec_sh);
+        if (rec_sh.i0 != kNoIndex) rec_sh.i0 += idx_offset;
+    }
+    unsigned ep = lane == 0 ? *TPB_CK(&mine->epoch) + 1u : 0u;
+    ep = __shfl_sync(kFull, ep, 0);
+    __syncwarp();
+    const int par = (int)(ep & 1u);
+    bool ok = true;
+    if (lane < world) {
+        *TPB_CK(&peers.p[lane]->slots[par][rank]) = rec_sh;                 // peer-to-peer stores
+        st_release_sys(TPB_CK(&peers.p[lane]->flags[rank]), ep);
+    }
+    __syncwarp();
+    if (lane == 0) TPB_RED_STAMP(4);
+    // the merge of the ranks' records: lane j holds rank j's, then the warp's fixed tree -- the order
+    // of finalize_kernel over the same records, so both exchange paths give the same bits
+    Acc all;
+    all.init();
+    all.finish_thread();
+    if (lane < world) {
+        // bounded wait for rank `lane`'s record of this epoch
+        int spin = 0;
+        while ((int)(ld_acquire_sys(TPB_CK(&mine->flags[lane])) - ep) < 0) {
+            if (++spin > max_polls) { ok = false; break; }
+            __nanosleep(100);
         }
+        if (ok) {
+            Acc o;
+            o.load(TPB_CK(&mine->slots[par][lane]));
+            all.merge(o);
+        }
+    }
+    ok = __all_sync(kFull, ok);
+    if (lane == 0) TPB_RED_STAMP(5);
+    warp_combine(all);
+    if (lane == 0) {
         *TPB_CK(&mine->epoch) = ep;
         if (!ok) {
             if (status) atomicMax(status, kErrExchange);
             if (ov) *TPB_CK(&ov[0]) = NAN;
             if (oi) *TPB_CK(&oi[0]) = -1;
         } else {
-            // the same rank-ordered merge on every GPU
-            Acc all;
-            all.init();
-            all.finish_thread();
-            for (int j = 0; j < world; ++j) {
-                Acc o;
-                o.load(TPB_CK(&mine->slots[par][j]));
-                all.merge(o);
-            }
             write_result(all, e, total_count, ov, oi, 0);
         }
+        TPB_RED_STAMP(6);
     }
 }
 
 }  // namespace tpb
+
+#ifdef TPB200_TRACE
+// Reads the seven stamps (nanoseconds of this GPU's %globaltimer) and re-arms them: slot 0 to the largest
+// value (it is a minimum), the others to 0.
+extern "C" int tpb200_debug_reduce_trace(unsigned long long* host, int n) {
+    if (n > 8) n = 8;
+    cudaError_t e = cudaMemcpyFromSymbol(host, tpb::g_red_trace, sizeof(unsigned long long) * n);
+    if (e != cudaSuccess) return (int)e;
+    unsigned long long init[8] = {~0ull, 0, 0, 0, 0, 0, 0, 0};
+    return (int)cudaMemcpyToSymbol(tpb::g_red_trace, init, sizeof(init));
+}
+#endif
 
 extern "C" size_t tpb200_exchange_buffer_bytes(void) { return sizeof(tpb::ExchangeBuf); }
 
