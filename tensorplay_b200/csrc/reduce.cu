@@ -79,21 +79,23 @@ template <class Acc>
 __global__ void __launch_bounds__(256)
 row_warp_kernel(const float* __restrict__ in, RowGeom g, Epilogue e, float* ov, long long* oi) {
     const int lane = threadIdx.x & 31;
-    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= g.rows) return;
-    const float* p = row_base(in, g, r);
-    Acc acc;
-    acc.init();
-    if (g.seglen >= 2048) {   // long runs: eight loads in flight per lane
-        for (long long s = 0; s < g.nseg; ++s)
-            scan_contig<8>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
-    } else {
-        for (long long s = 0; s < g.nseg; ++s)
-            scan_contig<4>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
+    const long long wpc = blockDim.x >> 5;
+    // the grid normally has a warp for every row; a smaller, persistent grid walks the rows
+    for (long long r = (long long)blockIdx.x * wpc + (threadIdx.x >> 5); r < g.rows; r += (long long)gridDim.x * wpc) {
+        const float* p = row_base(in, g, r);
+        Acc acc;
+        acc.init();
+        if (g.seglen >= 2048) {   // long runs: eight loads in flight per lane
+            for (long long s = 0; s < g.nseg; ++s)
+                scan_contig<8>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
+        } else {
+            for (long long s = 0; s < g.nseg; ++s)
+                scan_contig<4>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
+        }
+        acc.finish_thread();
+        warp_combine(acc);
+        if (lane == 0) write_result(acc, e, (double)g.nseg * (double)g.seglen, ov, oi, r);
     }
-    acc.finish_thread();
-    warp_combine(acc);
-    if (lane == 0) write_result(acc, e, (double)g.nseg * (double)g.seglen, ov, oi, r);
 }
 
 // ------------------------------------------------------------------ ROW: CTA per row -------
@@ -575,6 +577,11 @@ static int launch_plan(const Plan& pl, const float* in, Epilogue e, float* ov, l
                 if (a4 <= 10.0 && std::ceil(a4) / a4 < std::ceil(a8) / a8 - 0.02) wpc = 4;
             }
             unsigned grid = (unsigned)ceil_div(pl.row.rows, wpc);
+            // experiment switch: a persistent grid of that many CTAs per SM walking the rows.  Measured
+            // on [4096,4096] (1024 CTAs of 4 warps = 6.9 per SM by default, 12.5 us): 2 / 3 / 4 / 6 CTAs
+            // per SM 23.4 / 19.1 / 15.2 / 16.3 us -- never better than a warp per row.
+            int per_sm = 0;
+            if (env_int("TPB200_ROW_PERSIST", &per_sm) && per_sm >= 1) grid = std::min<unsigned>(grid, (unsigned)(sm_count() * per_sm));
             TPB_LAUNCH("row_warp_kernel", row_warp_kernel<Acc>, dim3(grid), wpc * 32, 0, st, in, pl.row, e, ov, oi);
             return TPB200_OK;
         }
