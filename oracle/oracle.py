@@ -7,7 +7,8 @@ Three checkers live here:
 
 * ``reduce`` / ``topk`` / ``topk_sort``: the plain-C restatement in tp_oracle.c
   (libtporacle.so), bit-identical to TensorPlay's CPU kernels
-  (p10/src/backend/cpu/ReductionKernels.cpp:72-855);
+  (p10/src/backend/cpu/ReductionKernels.cpp:72-855); top-k: parity unpinned (the reference has
+  no top-k; the contract is held by self-consistency only, see tp_oracle.c);
 * ``ref_reduce``: the reference's own compiled CPU path (oracle/_ref/libtpref.so, built by
   build_ref.sh where a TensorPlay checkout exists), used to validate the restatement and as
   the timed CPU baseline;

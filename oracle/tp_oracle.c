@@ -38,7 +38,11 @@
  * returns the mathematically meant result (first extremum along that dim, output laid out over
  * the kept dims in order), which is also what the reference's CUDA code computes.
  *
- * top-k is absent from the reference.  The contract restated here: the first k entries of the
+ * top-k: PARITY UNPINNED.  top-k is absent from the reference (no schema entry, kernel, binding, test
+ * or golden vector), so nothing of the reference can pin this part of the file: it is held only by
+ * self-consistency (sort form = heap form = numpy lexsort; k = 1 = argmax / argmin, which ARE pinned).
+ * softmax / log_softmax / median below are pinned like the reductions (compiled reference, fixture).
+ * The contract restated here: the first k entries of the
  * row stably sorted by value (descending when `largest`, else ascending), ties in ascending
  * index; -0.0 and +0.0 tie; NaN ranks after every number for both directions.  This follows the
  * only tie evidence in the reference, argmax/argmin's strict-compare scan (:727-735, :793-801),
