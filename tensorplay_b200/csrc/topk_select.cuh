@@ -415,7 +415,7 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
     float mx = NAN;   // fmaxf / fminf ignore a NaN operand
     for (int t = 0; t < sg.tpw; ++t) {
         load_tile(v, (long long)(t * NW + warp) * kWarpTile);
-        if (VEC && sg.prefetch && t == 0) {
+        if (VEC && sg.prefetch == 1 && t == 0) {
             // this warp's later sample tiles and its first scan tile: asked into L2 behind the loads of
             // the first tile, so that the loads that follow one another below find them there
             for (int u = 1; u <= sg.tpw; ++u) {
@@ -434,6 +434,17 @@ topk_select_kernel(const float* __restrict__ in, TopkGeom g, SelGeom sg, float* 
     const int first_scan = sg.tpw * NW;               // tiles [first_scan, first_scan + NW) are taken here
     const long long off_b = (long long)(first_scan + warp) * kWarpTile;
     load_tile(v, off_b);
+    if (VEC && sg.prefetch >= 2) {
+        // experiment (TPB200_SEL_PREFETCH = 2 | 3): while the threshold is worked out nothing else is
+        // loading; ask the tiles that the scan takes first after this one into L2 (one 128-byte line
+        // per lane covers a tile).  Measured, k = 1024: [64, 2^20] 62.7 us without, 63.4 us with two
+        // tiles per warp, 67.5 us with four; [512, 2^20] 356 / 354 / 353 us.  Off.
+        const int per_warp = sg.prefetch == 2 ? 2 : 4;
+        for (int u = 0; u < per_warp; ++u) {
+            const long long o = (long long)(first_scan + NW + u * NW + warp) * kWarpTile;
+            if (o + kWarpTile <= len) asm volatile("prefetch.global.L2 [%0];" ::"l"(slice + o + lane * 32));
+        }
+    }
     {
         unsigned key = rank_key<LARGEST>(mx);
 #pragma unroll
