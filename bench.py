@@ -230,6 +230,12 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
         b = 256 * 151936 * 4 + 256 * 50 * 12
         launches = tpb._lib.topk_plan_info([256, 151936], [151936, 1], 1, 50)["launches"]
         cases.append(Case("topk k=50 [256,151936]", lambda i: tpb.topk(xs[i % n], 50, -1, True, True, out=(ov, oi)), b, 256, launches, xs))
+        # the plain row reductions over the same batches: what reading these bytes once costs on this
+        # shape (256 rows of 608 KB), the floor that the top-k above is to be compared with
+        omx = torch.empty(256, device=dev)
+        oam = torch.empty(256, dtype=torch.int64, device=dev)
+        cases.append(Case("max dim=-1 [256,151936]", lambda i: tpb.max(xs[i % n], -1, out=omx), 256 * 151936 * 4 + 1024, 256, 1, xs))
+        cases.append(Case("argmax dim=-1 [256,151936]", lambda i: tpb.argmax(xs[i % n], -1, out=oam), 256 * 151936 * 4 + 2048, 256, 1, xs))
         osm = torch.empty(256, 151936, device=dev)
         cases.append(Case("softmax dim=-1 [256,151936]", lambda i: tpb.softmax(xs[i % n], -1, out=osm), 2 * 256 * 151936 * 4, 256, 1, xs))
     elif workload == "c1":

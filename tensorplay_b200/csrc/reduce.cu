@@ -508,6 +508,10 @@ static int make_plan(const void* in, int ndim, const int64_t* sizes, const int64
             long long want = std::max(1LL, (long long)sms * split_ctas_per_sm(fam) / outs);
             long long most = L / 16384;
             S = (int)std::max(1LL, std::min(std::min(want, most), 1LL << 20));
+            // At least one row per SM and a launch of tens of microseconds: a CTA per row, one launch and
+            // no partials.  Measured on [256,151936] over dim -1: 26.3 us (sum) / 26.8 us (max) against
+            // 28.2 / 29.9 us with every row split in two (two launches for a 27 us stream).
+            if (outs >= sms && outs * L * 4 <= (512LL << 20)) S = 1;
         }
         Strategy st;
         if (force == ST_ROW_SPLIT && g.nseg == 1 && outs <= 0x3fffff) { st = ST_ROW_SPLIT; S = std::max(S, 2); }
