@@ -102,8 +102,16 @@ row_warp_kernel(const float* __restrict__ in, RowGeom g, Epilogue e, float* ov, 
 // tps = threads that share one run (power of two).  With several runs per row the CTA is a
 // (tps x blockDim/tps) grid of threads: x walks along a run, y over runs, and loads of four
 // different runs are issued together so a thread always has 64 bytes in flight.
+// CTAs per SM that the register budget is cut for: three of 512 threads (40 registers) by default.
+// The product gets 64 registers (two CTAs per SM): squeezed into 40 the compiler no longer kept the
+// four loads of a step in flight together -- prod over dims (0,2) of [64,4096,512] 106.5 us with three
+// CTAs per SM, 85.0 us with two.  The variance is the other way round (94.0 us with three, 107.6 us
+// with two), the rest showed no difference.
+template <class Acc> struct RowCtaBounds { static constexpr int kMinCtas = 3; };
+template <> struct RowCtaBounds<ProdAcc> { static constexpr int kMinCtas = 2; };
+
 template <class Acc>
-__global__ void __launch_bounds__(512, 3)
+__global__ void __launch_bounds__(512, RowCtaBounds<Acc>::kMinCtas)
 row_cta_kernel(const float* __restrict__ in, RowGeom g, int tps, int vec_ok, Epilogue e, float* ov,
                long long* oi) {
     __shared__ Acc sm[32];
