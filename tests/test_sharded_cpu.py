@@ -70,7 +70,7 @@ def _worker(rank, world, port, total, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2])
+@pytest.mark.parametrize("world", [2, 4])
 def test_sharded_reducer_protocol_on_gloo(world):
     total = 100003
     mgr = mp.Manager()
