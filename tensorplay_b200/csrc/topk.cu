@@ -789,7 +789,7 @@ topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
 
     for (int i = tid; i < kRing; i += NW * 32) ring[i] = 0ull;
     if (tid < 64) sh.best[tid] = 0ull;
-    if (tid == 0) { sh.tau = 0ull; sh.cnt = 0u; sh.consumed = 0u; sh.next = NW; sh.done = 0; sh.err = 0; }
+    if (tid == 0) { sh.tau = 0ull; sh.cnt = 0u; sh.consumed = 0u; sh.next = 2 * NW; sh.done = 0; sh.err = 0; }   // tiles 0 .. 2 NW - 1 are taken by the bootstrap
 
     // Element j (0..31) of this lane in the tile at offset `off`: float4 number u*32+lane, component
     // c, j = 4u+c.
@@ -888,7 +888,14 @@ topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
     {
         float4 v[8];
         const long long off = (long long)warp * kWarpTile;
-        load_tile(v, off);
+        if (VEC && off + kWarpTile <= len) {
+            // with allocation in L1: the tile is read again below, once the threshold is known
+            const float* p = slice + off + lane * 4;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = ld_keep4(p + u * 128);
+        } else {
+            load_tile(v, off);
+        }
         float mx = NAN;   // fmaxf/fminf ignore a NaN operand: stays NaN only if the lane saw nothing else
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -896,6 +903,12 @@ topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
             else         mx = fminf(fminf(mx, v[u].x), fminf(fminf(v[u].y, v[u].z), v[u].w));
         }
         unsigned key = rank_key<LARGEST>(mx);
+        // The lane maxima are all the bootstrap needs of its tile: the registers take the warp's first
+        // streaming tile now, so that its loads are in flight while the threshold is worked out (the
+        // sort, two barriers and the rank count below were 2 us in which this CTA loaded nothing).
+        const long long off1 = (long long)(NW + warp) * kWarpTile;
+        const bool has1 = NW + warp < ntiles;
+        if (has1) load_tile(v, off1);
 #pragma unroll
         for (int size = 2; size <= 32; size <<= 1) {
 #pragma unroll
@@ -919,8 +932,16 @@ topk_smallk_kernel(const float* __restrict__ in, TopkGeom g, unsigned long long*
             if (above < k && k <= above + equal) sh.tau = (unsigned long long)my << 32;   // same value from every writer
         }
         __syncthreads();
-        const unsigned m = mask_of(v, *(volatile unsigned long long*)&sh.tau);
-        if (!drain(m, off)) failed = true;
+        const unsigned long long tau0 = *(volatile unsigned long long*)&sh.tau;
+        if (has1) {
+            const unsigned m1 = mask_of(v, tau0);
+            if (!drain(m1, off1)) failed = true;
+        }
+        if (!failed) {
+            load_tile(v, off);   // the bootstrap tile again (L1 / L2)
+            const unsigned m = mask_of(v, *(volatile unsigned long long*)&sh.tau);
+            if (!drain(m, off)) failed = true;
+        }
     }
 
     // ---- streaming loop: no barrier, tiles from a shared counter
