@@ -58,7 +58,10 @@ def check_softmax(cuda, x, dim, what=""):
 
 def test_softmax_rows_of_every_length(cuda):
     rng = np.random.default_rng(51)
-    for shape in ((5, 1), (7, 33), (300, 128), (64, 1000), (33, 1024), (9, 1025), (6, 4097), (17, 40000), (3, 5, 700)):
+    # (…, 1028) to (…, 16384): the register-resident CTA kernel with four and with eight float4 per
+    # thread, partly filled; 16388 and 40000: slices staged in shared memory; 1025 / 4097: unaligned rows
+    for shape in ((5, 1), (7, 33), (300, 128), (64, 1000), (33, 1024), (9, 1025), (6, 4097), (17, 40000), (3, 5, 700),
+                  (7, 1028), (5, 2048), (4, 5000), (3, 8192), (2, 8196), (4, 12000), (2, 16384), (2, 16388)):
         x = (rng.standard_normal(shape) * 5).astype(np.float32)
         check_softmax(cuda, x, -1)
     # rows not 16-byte aligned and a strided view (every other row of a wider matrix)
