@@ -75,27 +75,62 @@ __device__ __forceinline__ void add4(Acc& acc, const float4& v, long long b) {
 }
 
 // ------------------------------------------------------------------ ROW: warp per row ------
+template <class Acc, int UNROLL>
+__device__ __forceinline__ void row_warp_body(const float* __restrict__ in, const RowGeom& g, const Epilogue& e,
+                                              float* ov, long long* oi) {
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= g.rows) return;
+    // (A persistent grid walking the rows was measured on [4096,4096] -- 1024 CTAs of 4 warps = 6.9 per SM
+    //  here, 12.5 us: 2 / 3 / 4 / 6 CTAs per SM 23.4 / 19.1 / 15.2 / 16.3 us, never better than a warp per
+    //  row; and the loop alone cost the product 0.9 us.  Not kept.)
+    const float* p = row_base(in, g, r);
+    Acc acc;
+    acc.init();
+    for (long long s = 0; s < g.nseg; ++s)
+        scan_contig<UNROLL>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
+    acc.finish_thread();
+    warp_combine(acc);
+    if (lane == 0) write_result(acc, e, (double)g.nseg * (double)g.seglen, ov, oi, r);
+}
+// Runs of fewer than 2048 floats: four loads in flight per lane, and whatever registers the compiler
+// takes for 256 threads (48: short rows want warps, not registers -- [1048576, 64] and the variance of
+// [65536, 1024] are 20-40 % slower with 72).
 template <class Acc>
 __global__ void __launch_bounds__(256)
 row_warp_kernel(const float* __restrict__ in, RowGeom g, Epilogue e, float* ov, long long* oi) {
-    const int lane = threadIdx.x & 31;
-    const long long wpc = blockDim.x >> 5;
-    // the grid normally has a warp for every row; a smaller, persistent grid walks the rows
-    for (long long r = (long long)blockIdx.x * wpc + (threadIdx.x >> 5); r < g.rows; r += (long long)gridDim.x * wpc) {
-        const float* p = row_base(in, g, r);
-        Acc acc;
-        acc.init();
-        if (g.seglen >= 2048) {   // long runs: eight loads in flight per lane
-            for (long long s = 0; s < g.nseg; ++s)
-                scan_contig<8>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
-        } else {
-            for (long long s = 0; s < g.nseg; ++s)
-                scan_contig<4>(acc, p + s * g.seg_stride, g.seglen, s * g.seglen, lane, 32);
-        }
-        acc.finish_thread();
-        warp_combine(acc);
-        if (lane == 0) write_result(acc, e, (double)g.nseg * (double)g.seglen, ov, oi, r);
+    row_warp_body<Acc, 4>(in, g, e, ov, oi);
+}
+// Runs of 2048 floats and more: eight loads in flight per lane and up to 72 registers (seven 4-warp CTAs
+// per SM still fit).  At 48 the variance spilled and the others were squeezed: [4096,4096] var 12.9 ->
+// 12.2 us, sum 12.2 -> 11.9 us; [2048,8192] 14.0 -> 12.4 us.
+template <class Acc>
+__global__ void __maxnreg__(72)
+row_warp_long_kernel(const float* __restrict__ in, RowGeom g, Epilogue e, float* ov, long long* oi) {
+    row_warp_body<Acc, 8>(in, g, e, ov, oi);
+}
+
+// ------------------------------------------------------------------ ROW: several rows per warp
+// Contiguous rows of at most 256 floats: G = 4, 8 or 16 lanes share a row (a lane holds at most four
+// float4), so a warp works on 8, 4 or 2 rows at once and all 32 lanes load.  One warp per 64-float row
+// moved 0.96 TB/s on [1048576, 64]: half the lanes idle and five shuffle steps per 256 bytes.
+template <class Acc, int G>
+__global__ void __launch_bounds__(256)
+row_group_kernel(const float* __restrict__ in, RowGeom g, Epilogue e, float* ov, long long* oi) {
+    const int lane = threadIdx.x & 31, li = lane & (G - 1);
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long r = w * (32 / G) + lane / G;
+    // every lane takes part in the shuffles; lanes of a row past the end work on nothing
+    Acc acc;
+    acc.init();
+    if (r < g.rows) scan_contig<4>(acc, row_base(in, g, r), g.seglen, 0, li, G);
+    acc.finish_thread();
+#pragma unroll
+    for (int d = G / 2; d > 0; d >>= 1) {
+        Acc o = acc.shfl_down(d);
+        acc.merge(o);
     }
+    if (li == 0 && r < g.rows) write_result(acc, e, (double)g.seglen, ov, oi, r);
 }
 
 // ------------------------------------------------------------------ ROW: CTA per row -------
@@ -588,13 +623,18 @@ static int launch_plan(const Plan& pl, const float* in, Epilogue e, float* ov, l
                 const double a8 = (double)ceil_div(pl.row.rows, 8) / sms, a4 = (double)ceil_div(pl.row.rows, 4) / sms;
                 if (a4 <= 10.0 && std::ceil(a4) / a4 < std::ceil(a8) / a8 - 0.02) wpc = 4;
             }
+            if (pl.row.nseg == 1 && pl.row.seglen <= 256 && pl.row.rows >= 4096) {
+                const int G = pl.row.seglen <= 64 ? 4 : (pl.row.seglen <= 128 ? 8 : 16);
+                const long long warps = ceil_div(pl.row.rows, 32 / G);
+                const dim3 gg((unsigned)ceil_div(warps, 8));
+                if (G == 4)      TPB_LAUNCH("row_group_kernel", (row_group_kernel<Acc, 4>), gg, 256, 0, st, in, pl.row, e, ov, oi);
+                else if (G == 8) TPB_LAUNCH("row_group_kernel", (row_group_kernel<Acc, 8>), gg, 256, 0, st, in, pl.row, e, ov, oi);
+                else             TPB_LAUNCH("row_group_kernel", (row_group_kernel<Acc, 16>), gg, 256, 0, st, in, pl.row, e, ov, oi);
+                return TPB200_OK;
+            }
             unsigned grid = (unsigned)ceil_div(pl.row.rows, wpc);
-            // experiment switch: a persistent grid of that many CTAs per SM walking the rows.  Measured
-            // on [4096,4096] (1024 CTAs of 4 warps = 6.9 per SM by default, 12.5 us): 2 / 3 / 4 / 6 CTAs
-            // per SM 23.4 / 19.1 / 15.2 / 16.3 us -- never better than a warp per row.
-            int per_sm = 0;
-            if (env_int("TPB200_ROW_PERSIST", &per_sm) && per_sm >= 1) grid = std::min<unsigned>(grid, (unsigned)(sm_count() * per_sm));
-            TPB_LAUNCH("row_warp_kernel", row_warp_kernel<Acc>, dim3(grid), wpc * 32, 0, st, in, pl.row, e, ov, oi);
+            if (pl.row.seglen >= 2048) TPB_LAUNCH("row_warp_long_kernel", row_warp_long_kernel<Acc>, dim3(grid), wpc * 32, 0, st, in, pl.row, e, ov, oi);
+            else                       TPB_LAUNCH("row_warp_kernel", row_warp_kernel<Acc>, dim3(grid), wpc * 32, 0, st, in, pl.row, e, ov, oi);
             return TPB200_OK;
         }
         case ST_ROW_CTA: {

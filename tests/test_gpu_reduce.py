@@ -124,6 +124,24 @@ def test_small_shapes(cuda, shape, dimss):
                     check(cuda, x, op, dims, keepdim and dims is not None)
 
 
+def test_many_short_rows(cuda):
+    """Thousands of rows of at most 256 elements: several rows share a warp (4, 8 or 16 lanes per row);
+    ragged lengths, rows that are not 16-byte aligned, a strided view, ties and NaN."""
+    rng = np.random.default_rng(15)
+    for shape in ((5000, 64), (4100, 37), (8192, 256), (4097, 130), (6000, 1), (4500, 5), (70000, 16)):
+        x = rng.standard_normal(shape).astype(np.float32)
+        x[::7, 0] = x[::7, -1]                # ties between the ends of a row
+        if shape[1] > 2:
+            x[5, 1] = np.nan
+        for op in VALUE_OPS + EXT_OPS + ARG_OPS:
+            check(cuda, x, op, [1])
+            check(cuda, x, op, [-1], True)
+    wide = rng.standard_normal((5000, 80)).astype(np.float32)
+    for v in (wide[:, 1:65], wide[::2, 3:40]):
+        for op in ("sum", "var", "max", "argmin"):
+            check(cuda, v, op, [1])
+
+
 def test_strided_views(cuda):
     rng = np.random.default_rng(12)
     x = rng.standard_normal((6, 8, 10)).astype(np.float32)
