@@ -133,7 +133,7 @@ size_t tpb200_topk_workspace_bytes(int dtype, int ndim, const int64_t* sizes, co
 
 /* What the planner chose for a top-k call (no launch, no GPU needed); for benchmarks and tests.
  * No reference counterpart.  info[0..n_info) receives, in this order:
- *   0 scanning kernel (0 none, 1 whole-row sort, 2 rendezvous kernel, 3 ring kernel)
+ *   0 scanning kernel (0 none, 1 whole-row sort, 2 rendezvous kernel, 3 ring kernel, 4 warp per row)
  *   1 its slices per row            2 its warps per CTA
  *   3 1 if the sampled-threshold kernel runs first    4 its CTAs per row (cluster size)
  *   5 its warps per CTA             6 rank of the threshold key in the sample

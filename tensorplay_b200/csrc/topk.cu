@@ -1040,6 +1040,222 @@ topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long l
     }
 }
 
+// ------------------------------------------------------------------ short rows, small k ----
+// Rows of at most 4096 elements with k <= 64: one WARP per row (four rows per CTA), no barrier.
+//   1. every lane keeps the keys of its two best elements while the row is loaded (all 32 x 2 are
+//      distinct elements of the row); the k-th best of those 64 keys -- rank counting, two keys per
+//      lane -- is a threshold that at least k elements reach (key 0 = "take everything" when the row
+//      has fewer than k such keys);
+//   2. the row is walked again (registers for one tile, L1 / L2 otherwise) and the elements that reach
+//      the threshold are appended to the warp's 256-word buffer: per tile one mask per lane and one
+//      prefix sum over the lanes' counts;
+//   3. the buffer is sorted by the warp (bitonic network in shared memory) and the first k words are
+//      written out.
+// A row with more than 256 elements at or above its threshold (long runs of equal values) is done by
+// selection instead: k times the best word below the last one, the row read from L1 each time --
+// slow, exact, and only ever taken by such rows.
+// (Sorting every such row whole in shared memory, one CTA per row, ran [65536,1024] k = 10 in
+// 1454 us and [16384,4096] k = 50 in 1736 us: 3 % of the copy bandwidth.)
+constexpr int kWarpRowCap = 256;
+constexpr int kWarpRowMaxLen = 4096;
+
+template <bool LARGEST, bool VEC>
+__global__ void __launch_bounds__(128, 8)
+topk_warp_kernel(const float* __restrict__ in, TopkGeom g, float* __restrict__ out_val, long long* __restrict__ out_idx) {
+    __shared__ unsigned long long cand_all[4][kWarpRowCap];
+    __shared__ unsigned keys_all[4][64];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long r = (long long)blockIdx.x * 4 + warp;
+    if (r >= g.rows) return;
+    unsigned long long* cand = cand_all[warp];
+    unsigned* keys = keys_all[warp];
+    const float* row = topk_row(in, g, r);
+    const int len = (int)g.len, k = (int)g.k;
+    const int ntiles = (len + kWarpTile - 1) / kWarpTile;
+
+    // element j (0..31) of this lane in tile t: float4 number u * 32 + lane, component c, j = 4u + c
+    auto elem_of = [&](int t, int j) -> int { return t * kWarpTile + ((j >> 2) * 32 + lane) * 4 + (j & 3); };
+    auto load_tile = [&](float4 (&v)[8], int t) {
+        const int off = t * kWarpTile;
+        if (VEC && off + kWarpTile <= len) {
+            const float* p = row + off + lane * 4;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = ld_keep4(p + u * 128);
+        } else {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e0 = off + (u * 32 + lane) * 4;
+                float q[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) q[c] = e0 + c < len ? *TPB_CK(&row[(long long)(e0 + c) * g.es]) : NAN;
+                v[u] = make_float4(q[0], q[1], q[2], q[3]);
+            }
+        }
+    };
+
+    // ---- 1. the two best values per lane, compared as floats (-0.0 = +0.0 and NaN never better, as
+    // the keys order them); a lane that saw fewer than two numbers keeps the worst value
+    float4 v[8];
+    const float worst = LARGEST ? -INFINITY : INFINITY;
+    float f1 = worst, f2 = worst;
+    for (int t = 0; t < ntiles; ++t) {
+        load_tile(v, t);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const bool g1 = LARGEST ? q[c] > f1 : q[c] < f1;
+                const bool g2 = LARGEST ? q[c] > f2 : q[c] < f2;
+                f2 = g1 ? f1 : (g2 ? q[c] : f2);
+                f1 = g1 ? q[c] : f1;
+            }
+        }
+    }
+    // threshold key: the k-th best of the 32 best-per-lane values (k <= 32: a shuffle sort) or of all
+    // 64 (rank counting, two slots per lane).  At least k elements of the row reach it, unless the
+    // row has fewer than k numbers above the worst value -- then the count below falls short of k
+    // and everything is taken.
+    unsigned tkey = 0u;
+    if (k <= 32) {
+        unsigned key = rank_key<LARGEST>(f1);
+#pragma unroll
+        for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                const unsigned o = __shfl_xor_sync(kFull, key, stride);
+                const bool keep_max = ((lane & stride) == 0) == ((lane & size) == 0);
+                key = keep_max ? (o > key ? o : key) : (o < key ? o : key);
+            }
+        }
+        tkey = __shfl_sync(kFull, key, k - 1);      // descending: lane j holds the (j + 1)-th best
+    } else {
+        keys[lane] = rank_key<LARGEST>(f1);
+        keys[32 + lane] = rank_key<LARGEST>(f2);
+        __syncwarp();
+        const unsigned a = keys[lane], b = keys[32 + lane];
+        int ra = 0, rb = 0;   // how many of the 64 slots rank before this one (ties by slot number)
+        for (int j = 0; j < 64; ++j) {
+            const unsigned o = keys[j];
+            ra += (o > a || (o == a && j < lane)) ? 1 : 0;
+            rb += (o > b || (o == b && j < 32 + lane)) ? 1 : 0;
+        }
+        unsigned mine = ra == k - 1 ? a : (rb == k - 1 ? b : 0u);   // exactly one slot has rank k - 1
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) mine |= __shfl_xor_sync(kFull, mine, d);
+        tkey = mine;
+    }
+
+    // ---- 2. the elements that reach the threshold: one float compare each (ties and both zeros pass,
+    // NaN does not); a threshold key of 0 takes everything
+    int n = 0;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        const bool all = tkey == 0u;
+        const float tvf = key_value<LARGEST>(tkey);
+        n = 0;
+        for (int t = 0; t < ntiles; ++t) {
+            if (ntiles > 1 || attempt > 0) load_tile(v, t);        // one tile: still in the registers
+            unsigned mask = 0u;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const bool pass = all || (LARGEST ? q[c] >= tvf : q[c] <= tvf);
+                    mask |= (pass ? 1u : 0u) << (4 * u + c);
+                }
+            }
+            // padding of a ragged last tile reads as NaN: only "take everything" can let it through
+            if (all && (t + 1) * kWarpTile > len) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (elem_of(t, j) >= len) mask &= ~(1u << j);
+            }
+            const int cnt = __popc(mask);
+            int incl = cnt;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(kFull, incl, d);
+                if (lane >= d) incl += o;
+            }
+            const int total = __shfl_sync(kFull, incl, 31);
+            int pos = n + incl - cnt;
+            if (n + total <= kWarpRowCap) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int j = 4 * u + c;
+                        if (mask & (1u << j)) cand[pos++] = rank_word<LARGEST>(q[c], (unsigned)elem_of(t, j));
+                    }
+                }
+            }
+            n += total;
+        }
+        if (n >= k || all) break;
+        tkey = 0u;      // fewer than k numbers above the worst value: NaN and the worst value belong to the answer
+    }
+    float* ov = out_val + r * k;
+    long long* oi = out_idx + r * k;
+    auto emit = [&](int j, unsigned long long w) {
+        const unsigned idx = word_index(w);
+        const unsigned key = (unsigned)(w >> 32);
+        float val = key_value<LARGEST>(key);
+        // the key folds -0.0 onto +0.0 and all NaNs onto one rank: those come from the row
+        if (key == 0u || val == 0.0f) val = *TPB_CK(&row[(long long)idx * g.es]);
+        *TPB_CK(&oi[j]) = (long long)idx;
+        *TPB_CK(&ov[j]) = val;
+    };
+    if (n <= kWarpRowCap) {
+        // ---- 3. sort and write
+        int N = 32;
+        while (N < n) N <<= 1;
+        for (int i = n + lane; i < N; i += 32) cand[i] = 0ull;
+        __syncwarp();
+        for (int size = 2; size <= N; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                for (int q = lane; q < (N >> 1); q += 32) {
+                    const int lo = ((q & ~(stride - 1)) << 1) | (q & (stride - 1));
+                    const int hi = lo | stride;
+                    const bool desc = (lo & size) == 0;
+                    const unsigned long long x = cand[lo], y = cand[hi];
+                    if ((x < y) == desc) { cand[lo] = y; cand[hi] = x; }
+                }
+                __syncwarp();
+            }
+        }
+        for (int j = lane; j < k; j += 32) emit(j, cand[j]);
+        return;
+    }
+    // ---- selection for rows with long runs of equal values: k times the best word below the last
+    unsigned long long prev = ~0ull;
+    for (int j = 0; j < k; ++j) {
+        unsigned long long best = 0ull;
+        for (int t = 0; t < ntiles; ++t) {
+            load_tile(v, t);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int e = elem_of(t, 4 * u + c);
+                    if (e < len) {
+                        const unsigned long long w = rank_word<LARGEST>(q[c], (unsigned)e);
+                        if (w < prev && w > best) best = w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const unsigned long long o = __shfl_xor_sync(kFull, best, d);
+            best = o > best ? o : best;
+        }
+        if (lane == 0) emit(j, best);
+        prev = best;
+    }
+}
+
 // ------------------------------------------------------------------ global merge -----------
 // Candidates carry 64-bit tensor-global indices, so the order is on (key, index) pairs.
 template <bool LARGEST>
@@ -1101,7 +1317,7 @@ __device__ __forceinline__ int pow2_ceil_dev(int v) { return v <= 1 ? 1 : 1 << (
 namespace tpb {
 
 // ------------------------------------------------------------------ planner ----------------
-enum TopkPath { TK_NONE, TK_SORTROW, TK_STREAM, TK_SMALLK };
+enum TopkPath { TK_NONE, TK_SORTROW, TK_STREAM, TK_SMALLK, TK_WARPROW };
 
 struct TopkPlan {
     TopkPath path = TK_NONE;
@@ -1257,6 +1473,11 @@ static int topk_plan(const void* in, int ndim, const int64_t* sizes, const int64
     const bool force_sort = force && std::string(force) == "sort";
     const bool force_stream = force && std::string(force) == "stream";
 
+    if (len <= kWarpRowMaxLen && k <= 64 && !force_sort && !force_stream) {
+        if (ceil_div(rows, 4) > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
+        pl->path = TK_WARPROW;      // a warp per row, one launch, no scratch
+        return TPB200_OK;
+    }
     if ((len <= 4096 && !force_stream) || k > kMaxStreamK || (force_sort && len <= kMaxSortRow)) {
         if (len > kMaxSortRow)
             return fail(TPB200_ERR_UNSUPPORTED, "k > %d is only supported on rows of at most %d elements", kMaxStreamK, kMaxSortRow);
@@ -1374,6 +1595,12 @@ template <bool LARGEST>
 static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long* oi, void* ws,
                        cudaStream_t st) {
     const TopkGeom& g = pl.g;
+    if (pl.path == TK_WARPROW) {
+        const dim3 grid((unsigned)ceil_div(g.rows, 4));
+        if (pl.vec) TPB_LAUNCH("topk_warp_kernel", (topk_warp_kernel<LARGEST, true>), grid, 128, 0, st, in, g, ov, oi);
+        else        TPB_LAUNCH("topk_warp_kernel", (topk_warp_kernel<LARGEST, false>), grid, 128, 0, st, in, g, ov, oi);
+        return TPB200_OK;
+    }
     if (pl.path == TK_SORTROW) {
         size_t sm = (size_t)pl.N * 8;
         int rc = allow_smem(topk_sort_kernel<LARGEST, true>, sm);

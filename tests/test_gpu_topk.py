@@ -42,6 +42,48 @@ def test_small_rows_sorted_whole(cuda):
                 check_topk(cuda, x, k, -1, largest, oracle="sort")
 
 
+def test_warp_per_row_kernel(cuda):
+    """Rows of at most 4096 elements with k <= 64 (a warp per row): every tile count, ragged lengths,
+    strided and unaligned rows, k at both ends, ties, NaN and zeros of both signs, and rows with more
+    than 256 elements at the threshold (all equal, two values), which take the selection path."""
+    import torch
+    import tensorplay_b200 as tpb
+    from tensorplay_b200 import _lib
+    rng = np.random.default_rng(29)
+    assert _lib.topk_plan_info([4100, 1000], [1000, 1], 1, 10)["scan_kernel"] == 4
+    for shape, ks in [((4100, 100), [1, 10, 64]), ((300, 1000), [1, 7, 33, 64]), ((70, 1024), [64]), ((50, 1025), [5, 40]),
+                      ((33, 2048), [50]), ((17, 3000), [32, 64]), ((9, 4096), [1, 64]), ((5, 40), [40]), ((3, 64), [64]),
+                      ((6, 70), [64])]:
+        x = rng.standard_normal(shape).astype(np.float32)
+        x[::3, 1] = x[::3, 0]                         # a tie at the front of some rows
+        if shape[1] > 8:
+            x[1, 3] = np.nan
+            x[2, 5] = 0.0
+            x[2, 6] = -0.0
+        for k in ks:
+            for largest in (True, False):
+                check_topk(cuda, x, k, -1, largest, oracle="sort")
+    # tie-heavy rows: more than 256 elements reach the threshold
+    for x in (np.ones((6, 3000), dtype=np.float32), rng.integers(0, 2, (8, 4096)).astype(np.float32),
+              rng.integers(0, 3, (5, 700)).astype(np.float32)):
+        for k in (1, 20, 64):
+            for largest in (True, False):
+                check_topk(cuda, x, k, -1, largest, oracle="sort")
+    # a strided view (every other column) and rows that are not 16-byte aligned
+    from oracle import oracle as O
+    wide = rng.standard_normal((200, 2051)).astype(np.float32)
+    wg = torch.from_numpy(wide).to(cuda)
+    for vn, vg in ((wide[:, ::2], wg[:, ::2]), (wide[:, 1:1026], wg[:, 1:1026]), (wide[::2, 3:], wg[::2, 3:])):
+        gv, gi = tpb.topk(vg, 16, -1, True, True)        # the views are read in place
+        wv, wi = O.topk_sort(np.ascontiguousarray(vn), 16, -1, True)
+        assert_index_equal(gi.cpu().numpy(), wi, "strided view")
+        assert_bits_equal(gv.cpu().numpy(), wv, "strided view")
+    # a middle dim
+    y = rng.standard_normal((12, 500, 7)).astype(np.float32)
+    check_topk(cuda, y, 9, 1, False, oracle="sort")
+    assert _lib.device_status() == 0
+
+
 def test_k1_equals_argmax(cuda):
     import torch
     import tensorplay_b200 as tpb
