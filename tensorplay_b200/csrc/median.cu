@@ -10,7 +10,11 @@
 //   pick     one CTA scans the 2048 bins, finds the bin that holds the wanted rank, extends the
 //            prefix, reduces the rank and clears the bins for the next sweep.
 // After the third pick the prefix is the key of the median; its value is written to the output.
-// Everything stays on the stream: the state lives in the caller's workspace.
+// The second sweep also copies the elements that match the first digit (the median's bin of the first
+// histogram: a fraction of a percent of ordinary data) into a buffer of 2^20 floats behind the state;
+// the third sweep reads that buffer instead of the input when everything fitted, so the input is
+// read twice, not three times.  Everything stays on the stream: state and buffer live in the caller's
+// workspace.
 #define TPB_FILE_ID 5
 #include "common.cuh"
 #include "host_util.h"
@@ -22,11 +26,16 @@ namespace tpb {
 constexpr int kMedBins = 2048;
 constexpr int kMedThreads = 512;
 
+constexpr unsigned kMedCand = 1u << 20;    // floats kept from the second sweep
+constexpr int kMedKeep = 2048;             // of which per CTA, staged in shared memory
+
 struct MedianState {
     unsigned long long rank;      // rank still wanted among the keys that match the prefix
     unsigned prefix;              // digits found so far, right-aligned
-    unsigned pad;
+    unsigned kept;                // elements the second sweep wanted to keep (may exceed kMedCand: then none are used)
     unsigned hist[kMedBins];
+    unsigned pad2[2];
+    float cand[kMedCand];
 };
 
 __device__ __forceinline__ unsigned median_key(float x) {
@@ -56,8 +65,11 @@ template <bool CONTIG>
 __global__ void __launch_bounds__(kMedThreads)
 median_hist_kernel(const float* __restrict__ in, long long n, MedGeom g, int pass, MedianState* st) {
     __shared__ unsigned hist[kMedBins];
+    __shared__ float keep[kMedKeep];        // second sweep: this CTA's elements for the last sweep
+    __shared__ unsigned keep_n, keep_over, keep_base;
     const int tid = threadIdx.x;
     for (int i = tid; i < kMedBins; i += kMedThreads) hist[i] = 0u;
+    if (tid == 0) { keep_n = 0u; keep_over = 0u; keep_base = 0u; }
     __syncthreads();
     int shift, bits;
     digit_of_pass(pass, &shift, &bits);
@@ -66,10 +78,22 @@ median_hist_kernel(const float* __restrict__ in, long long n, MedGeom g, int pas
     const int above = shift + bits;             // key >> above must equal the prefix (pass 0: nothing above)
     auto count = [&](float x) {
         const unsigned key = median_key(x);
-        if (pass == 0 || (key >> above) == prefix) atomicAdd(&hist[(key >> shift) & mask], 1u);
+        if (pass == 0 || (key >> above) == prefix) {
+            atomicAdd(&hist[(key >> shift) & mask], 1u);
+            if (pass == 1 && *(volatile unsigned*)&keep_over == 0u) {
+                // kept in shared memory first: one global atomic per CTA at the end.  A CTA that finds more
+                // than its buffer holds (heavy ties) gives up keeping, and the last sweep reads the input.
+                const unsigned p = atomicAdd(&keep_n, 1u);
+                if (p < (unsigned)kMedKeep) keep[p] = x; else *(volatile unsigned*)&keep_over = 1u;
+            }
+        }
     };
     const long long gtid = (long long)blockIdx.x * kMedThreads + tid, gthreads = (long long)gridDim.x * kMedThreads;
-    if (CONTIG) {
+    const unsigned kept = pass == 2 ? *TPB_CK(&st->kept) : 0u;
+    if (pass == 2 && kept <= kMedCand) {
+        // everything that matches the first digit is in the buffer: the input is not read again
+        for (long long i = gtid; i < (long long)kept; i += gthreads) count(*TPB_CK(&st->cand[i]));
+    } else if (CONTIG) {
         // 16-byte loads on the aligned body, scalars at both ends
         long long head = (long long)((4 - (((uintptr_t)in >> 2) & 3)) & 3);
         if (head > n) head = n;
@@ -104,6 +128,14 @@ median_hist_kernel(const float* __restrict__ in, long long n, MedGeom g, int pas
     for (int i = tid; i < kMedBins; i += kMedThreads) {
         const unsigned c = hist[i];
         if (c) atomicAdd(TPB_CK(&st->hist[i]), c);
+    }
+    if (pass == 1) {
+        const unsigned mine = keep_over ? 0u : keep_n;
+        if (tid == 0) keep_base = atomicAdd(TPB_CK(&st->kept), keep_over ? kMedCand + 1u : mine);   // an overflow spoils the buffer for everybody
+        __syncthreads();
+        const unsigned base = keep_base;
+        for (unsigned i = tid; i < mine; i += kMedThreads)
+            if (base + i < kMedCand) *TPB_CK(&st->cand[base + i]) = keep[i];
     }
 }
 
@@ -150,7 +182,7 @@ __global__ void median_init_kernel(MedianState* st, unsigned long long rank, flo
     if (tid == 0) {
         *TPB_CK(&st->rank) = rank;
         *TPB_CK(&st->prefix) = 0u;
-        *TPB_CK(&st->pad) = 0u;
+        *TPB_CK(&st->kept) = 0u;
         if (empty) *TPB_CK(&out[0]) = NAN;   // the reference returns NaN for an empty tensor (ReductionKernels.cpp:877)
     }
 }
