@@ -164,7 +164,8 @@ int tpb200_softmax(int log, const void* in, int dtype, int ndim, const int64_t* 
  * values, i.e. the lower middle one for even n; NaN for an empty tensor.  Here NaNs rank after all
  * numbers (the reference's std::nth_element leaves their place undefined); -0.0 and +0.0 are one
  * value and +0.0 is returned for it.  `out` receives one float32.  Any strided view; the workspace
- * (tpb200_median_workspace_bytes(), 8-byte aligned) needs no initialisation.
+ * (tpb200_median_workspace_bytes(), about 4 MB: the selection state and a buffer for the elements
+ * around the median; 8-byte aligned) needs no initialisation.
  */
 int tpb200_median(const void* in, int dtype, int ndim, const int64_t* sizes, const int64_t* strides,
                   void* out, void* workspace, size_t workspace_bytes, void* stream);
