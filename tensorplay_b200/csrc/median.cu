@@ -79,6 +79,8 @@ median_hist_kernel(const float* __restrict__ in, long long n, MedGeom g, int pas
     auto count = [&](float x) {
         const unsigned key = median_key(x);
         if (pass == 0 || (key >> above) == prefix) {
+            // (adding once per group of lanes with the same bin, found with __match_any_sync, was measured:
+            //  118 us per call against 51 us -- the match costs more than the conflicts it removes)
             atomicAdd(&hist[(key >> shift) & mask], 1u);
             if (pass == 1 && *(volatile unsigned*)&keep_over == 0u) {
                 // kept in shared memory first: one global atomic per CTA at the end.  A CTA that finds more
