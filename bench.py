@@ -45,7 +45,7 @@ NOMINAL_PEAK_GBS = 8000.0
 # DRAM traffic per launch of the dominant kernel from one ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum).  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    "c2": 155_654_912 + 4_059_392,   # topk_smallk_kernel, [256,151936] k = 50 (algorithmic 155.74 MB)
+    "c2": 155_666_688 + 3_863_296,   # topk_smallk_kernel, [256,151936] k = 50 (algorithmic 155.74 MB)
     "c1": 67_143_424 + 418_816,      # row_warp_kernel
     "c3": 536_887_808 + 6_670_848,   # col_kernel
     # topk_select_kernel captured on [64, 2^20] k = 1024 (269.80 MB read + 3.39 MB written for an
@@ -329,7 +329,7 @@ def build_cases(torch, tpb, dev, workload: str, rank: int, world: int, seed: int
 # hundred MB (larger than L2, so DRAM counters mean something; small enough for a many-pass capture).
 PROFILE_CASES = ("topk_c2", "topk_64x1048576_k1024", "sum_c1", "softmax_c1", "softmax_c2", "median_c1",
                  "sum02_16x4096x512", "std02_16x4096x512", "prod02_16x4096x512", "permute_copy_16x4096x512",
-                 "sum_2p28")
+                 "sum_2p28", "topk_65536x1024_k10", "sum_1048576x64")
 
 
 def build_profile_case(torch, tpb, dev, name: str):
@@ -368,6 +368,15 @@ def build_profile_case(torch, tpb, dev, name: str):
         ov = torch.empty(4096, device=dev)
         fn = {"sum02": tpb.sum, "std02": tpb.std, "prod02": tpb.prod}[name.split("_")[0]]
         return Case(f"{name.split('_')[0][:-2]} dims=(0,2) [16,4096,512]", lambda i: fn(xs[i % 2], [0, 2], out=ov), inb + 16384, 4096, 1, xs)
+    if name == "topk_65536x1024_k10":
+        xs = [torch.randn(65536, 1024, device=dev, generator=gen) for _ in range(2)]
+        ov = torch.empty(65536, 10, device=dev)
+        oi = torch.empty(65536, 10, dtype=torch.int64, device=dev)
+        return Case("topk k=10 [65536,1024]", lambda i: tpb.topk(xs[i % 2], 10, -1, True, True, out=(ov, oi)), 65536 * (1024 * 4 + 10 * 12), 65536, 1, xs)
+    if name == "sum_1048576x64":
+        xs = [torch.randn(1 << 20, 64, device=dev, generator=gen) for _ in range(2)]
+        ov = torch.empty(1 << 20, device=dev)
+        return Case("sum dim=-1 [1048576,64]", lambda i: tpb.sum(xs[i % 2], -1, out=ov), (1 << 20) * (64 * 4 + 4), 1 << 20, 1, xs)
     if name == "sum_2p28":
         x = gen_c4(torch, dev, gen, 1 << 28)
         return Case("sum whole tensor 2^28", lambda i: tpb.sum(x), (1 << 30) + 4, 1, 2, [x])

@@ -1059,7 +1059,7 @@ topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long l
 constexpr int kWarpRowCap = 256;
 constexpr int kWarpRowMaxLen = 4096;
 
-template <bool LARGEST, bool VEC>
+template <bool LARGEST, bool VEC, bool TWO /* k > 32: two values per lane enter the threshold */>
 __global__ void __launch_bounds__(128, 8)
 topk_warp_kernel(const float* __restrict__ in, TopkGeom g, float* __restrict__ out_val, long long* __restrict__ out_idx) {
     __shared__ unsigned long long cand_all[4][kWarpRowCap];
@@ -1105,10 +1105,14 @@ topk_warp_kernel(const float* __restrict__ in, TopkGeom g, float* __restrict__ o
             const float q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const bool g1 = LARGEST ? q[c] > f1 : q[c] < f1;
-                const bool g2 = LARGEST ? q[c] > f2 : q[c] < f2;
-                f2 = g1 ? f1 : (g2 ? q[c] : f2);
-                f1 = g1 ? q[c] : f1;
+                if (TWO) {
+                    const bool g1 = LARGEST ? q[c] > f1 : q[c] < f1;
+                    const bool g2 = LARGEST ? q[c] > f2 : q[c] < f2;
+                    f2 = g1 ? f1 : (g2 ? q[c] : f2);
+                    f1 = g1 ? q[c] : f1;
+                } else {
+                    f1 = LARGEST ? fmaxf(f1, q[c]) : fminf(f1, q[c]);   // a NaN operand is ignored
+                }
             }
         }
     }
@@ -1117,7 +1121,7 @@ topk_warp_kernel(const float* __restrict__ in, TopkGeom g, float* __restrict__ o
     // row has fewer than k numbers above the worst value -- then the count below falls short of k
     // and everything is taken.
     unsigned tkey = 0u;
-    if (k <= 32) {
+    if (!TWO) {
         unsigned key = rank_key<LARGEST>(f1);
 #pragma unroll
         for (int size = 2; size <= 32; size <<= 1) {
@@ -1206,6 +1210,22 @@ topk_warp_kernel(const float* __restrict__ in, TopkGeom g, float* __restrict__ o
         *TPB_CK(&oi[j]) = (long long)idx;
         *TPB_CK(&ov[j]) = val;
     };
+    if (n <= 32) {
+        // ---- 3a. at most one word per lane: sorted with shuffles, no shared-memory traffic
+        __syncwarp();
+        unsigned long long w = lane < n ? cand[lane] : 0ull;
+#pragma unroll
+        for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                const unsigned long long o = __shfl_xor_sync(kFull, w, stride);
+                const bool keep_max = ((lane & stride) == 0) == ((lane & size) == 0);
+                w = keep_max ? (o > w ? o : w) : (o < w ? o : w);
+            }
+        }
+        if (lane < k) emit(lane, w);
+        return;
+    }
     if (n <= kWarpRowCap) {
         // ---- 3. sort and write
         int N = 32;
@@ -1597,8 +1617,13 @@ static int topk_launch(const TopkPlan& pl, const float* in, float* ov, long long
     const TopkGeom& g = pl.g;
     if (pl.path == TK_WARPROW) {
         const dim3 grid((unsigned)ceil_div(g.rows, 4));
-        if (pl.vec) TPB_LAUNCH("topk_warp_kernel", (topk_warp_kernel<LARGEST, true>), grid, 128, 0, st, in, g, ov, oi);
-        else        TPB_LAUNCH("topk_warp_kernel", (topk_warp_kernel<LARGEST, false>), grid, 128, 0, st, in, g, ov, oi);
+        if (g.k > 32) {
+            if (pl.vec) TPB_LAUNCH("topk_warp_kernel", (topk_warp_kernel<LARGEST, true, true>), grid, 128, 0, st, in, g, ov, oi);
+            else        TPB_LAUNCH("topk_warp_kernel", (topk_warp_kernel<LARGEST, false, true>), grid, 128, 0, st, in, g, ov, oi);
+        } else {
+            if (pl.vec) TPB_LAUNCH("topk_warp_kernel", (topk_warp_kernel<LARGEST, true, false>), grid, 128, 0, st, in, g, ov, oi);
+            else        TPB_LAUNCH("topk_warp_kernel", (topk_warp_kernel<LARGEST, false, false>), grid, 128, 0, st, in, g, ov, oi);
+        }
         return TPB200_OK;
     }
     if (pl.path == TK_SORTROW) {
