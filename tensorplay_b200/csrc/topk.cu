@@ -1056,6 +1056,10 @@ topk_sort_kernel(const float* __restrict__ in, TopkGeom g, const unsigned long l
 // slow, exact, and only ever taken by such rows.
 // (Sorting every such row whole in shared memory, one CTA per row, ran [65536,1024] k = 10 in
 // 1454 us and [16384,4096] k = 50 in 1736 us: 3 % of the copy bandwidth.)
+// The same idea for thousands of rows of 4 K to 64 K elements -- a warp per row in ONE pass, threshold
+// from the first tile and raised by cuts of the warp's buffer -- was built, passed the parity tests and
+// measured 108 us on [4096,16384] k = 50 against 86.5 us for the ring kernel with a CTA per row: a warp
+// has one 4 KB tile in flight and nothing to do while it waits.  Not kept.
 constexpr int kWarpRowCap = 256;
 constexpr int kWarpRowMaxLen = 4096;
 
@@ -1160,13 +1164,15 @@ topk_warp_kernel(const float* __restrict__ in, TopkGeom g, float* __restrict__ o
         for (int t = 0; t < ntiles; ++t) {
             if (ntiles > 1 || attempt > 0) load_tile(v, t);        // one tile: still in the registers
             unsigned mask = 0u;
+            if (all || (LARGEST ? f1 >= tvf : f1 <= tvf)) {        // a lane whose best value misses has nothing
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                for (int u = 0; u < 8; ++u) {
+                    const float q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const bool pass = all || (LARGEST ? q[c] >= tvf : q[c] <= tvf);
-                    mask |= (pass ? 1u : 0u) << (4 * u + c);
+                    for (int c = 0; c < 4; ++c) {
+                        const bool pass = all || (LARGEST ? q[c] >= tvf : q[c] <= tvf);
+                        mask |= (pass ? 1u : 0u) << (4 * u + c);
+                    }
                 }
             }
             // padding of a ragged last tile reads as NaN: only "take everything" can let it through
