@@ -452,7 +452,11 @@ extern "C" int tpb200_softmax(int log, const void* in, int dtype, int ndim, cons
         if (rows * S > 0x7fffffffLL) return fail(TPB200_ERR_UNSUPPORTED, "too many rows for one launch");
         const int threads = C / S >= 8192 ? 512 : (C / S >= 2048 ? 256 : 128);
         const dim3 grid((unsigned)(rows * S));
-        const bool stage = vec && chunk <= kStageMax;
+        int stage_on = 1;
+        // experiment switch: 0 never keeps the slice in shared memory ([256,151936] with eight CTAs per row:
+        // 84 us staged, 91 us not -- the clusters of eight cost more than the second read saves either way)
+        env_int("TPB200_SOFTMAX_STAGE", &stage_on);
+        const bool stage = vec && chunk <= kStageMax && stage_on != 0;
         const size_t smem = stage ? (size_t)chunk * sizeof(float) : 0;
         cudaError_t e = cudaSuccess;
 #define TPB_SM_LONG(LOGV, STAGEV)                                                                                  \
